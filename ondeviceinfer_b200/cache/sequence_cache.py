@@ -96,8 +96,9 @@ class CacheView:
 
 
 class SequenceCache:
-    """``needs[e]`` is the tuple of needs of order entry ``e`` (empty for an entry that
-    reads another entry's cache); ``cache_from[e]`` names that other entry or is None."""
+    """``needs[e]`` is the tuple of needs of order entry ``e``; ``cache_from[e]`` names another entry whose keys
+    and values this entry reads instead of keeping its own (its ``needs`` then hold no :class:`KVNeed`), or is
+    None.  Fixed-size state is never shared: an entry's :class:`StateNeed` s are its own either way."""
 
     def __init__(self, needs: Sequence[Tuple[object, ...]], cache_from: Sequence[Optional[int]], *,
                  dtype: torch.dtype, device, max_tokens: int, max_seqs: int,
@@ -121,8 +122,9 @@ class SequenceCache:
         kv_owners: Dict[KVNeed, List[int]] = {}
         state_owners: Dict[StateNeed, List[int]] = {}
         for entry, entry_needs in enumerate(needs):
-            if cache_from[entry] is not None:
-                continue
+            if cache_from[entry] is not None and any(isinstance(need, KVNeed) for need in entry_needs):
+                raise ValueError(f"order entry {entry} reads the keys and values of entry {cache_from[entry]} and "
+                                 "asks for a store of its own")
             if len(set(entry_needs)) != len(entry_needs):
                 raise ValueError(f"order entry {entry} names the same cache need twice (give states a name): {entry_needs}")
             for need in entry_needs:
@@ -150,8 +152,8 @@ class SequenceCache:
                     pos = group.owners.index(source)
                     view.kv_group, view.keys, view.values = group, group.keys(pos), group.values(pos)
             by_need = {group.need: group for group in self.state_groups}
-            view.states = tuple(by_need[need].data[by_need[need].owners.index(source)]
-                                for need in needs[source] if isinstance(need, StateNeed))
+            view.states = tuple(by_need[need].data[by_need[need].owners.index(entry)]
+                                for need in needs[entry] if isinstance(need, StateNeed))
             view.state = view.states[0] if view.states else None
             self._views.append(view)
 

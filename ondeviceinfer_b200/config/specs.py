@@ -26,13 +26,15 @@ class RMSNormSpec:
 
     ``weight_offset``: the row is scaled by ``weight_offset + weight`` (1.0 for a weight that is stored as its
     deviation from one).  ``scale_in_fp32``: the scaling is done in fp32 before the one rounding to the compute
-    dtype, y = cast(x * rsqrt(mean(x^2) + eps) * (weight_offset + weight))."""
+    dtype, y = cast(x * rsqrt(mean(x^2) + eps) * (weight_offset + weight)).  ``scalar_weight``: the stored weight
+    is a single number (a tensor without dimensions) that scales every coordinate."""
 
     size: int
     eps: float
     weight_name: str  # full checkpoint name of the [size] weight
     weight_offset: float = 0.0
     scale_in_fp32: bool = False
+    scalar_weight: bool = False
 
 
 @dataclass(frozen=True)
@@ -41,13 +43,19 @@ class RotarySpec:
     i + rotary_dim / 2 (half-split), or, with ``interleaved``, lane 2i with lane 2i + 1; the angle of pair i at
     position p is p * f_i, f_i = theta^(-2i / rotary_dim).  ``scaling`` = (factor, low, high, original) slows the
     long wavelengths: with l = 2 pi / f_i, f_i stays where l < original / high, becomes f_i / factor where
-    l > original / low, and in between is (1 - s) f_i / factor + s f_i with s = (original / l - low) / (high - low)."""
+    l > original / low, and in between is (1 - s) f_i / factor + s f_i with s = (original / l - low) / (high - low).
+    ``index_ramp`` = (factor, original, fast, slow) is another way to slow them, by a ramp over the pair index: with
+    n(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the index of the pair that makes t turns over
+    ``original`` positions, lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1) and
+    s_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is s_i f_i / factor + (1 - s_i) f_i, and cos and
+    sin are both multiplied by 0.1 ln(factor) + 1."""
 
     head_dim: int
     theta: float
     rotary_dim: Optional[int] = None  # None: the whole head
     interleaved: bool = False
     scaling: Optional[Tuple[float, float, float, float]] = None
+    index_ramp: Optional[Tuple[float, float, float, float]] = None
 
     @property
     def dim(self) -> int:
@@ -97,7 +105,11 @@ class CappedAttentionSpec:
     ``unit_norm_eps`` not None, every q and k head is divided by sqrt(mean of its squares + eps) (no weight).
     score = q . k * ``scale``; with ``softcap`` c not None, score <- c tanh(score / c); ordinary softmax over the
     visible keys: all of 0..p, or with ``window`` w the last w of them (p itself included).  All of this in fp32.
-    ``names`` maps the roles q, k, v, o to tensor names below ``prefix``."""
+    ``sink``: the softmax has one more term, of score 0 and without a value: p_j = exp(s_j) / (1 + sum_k exp(s_k)).
+    ``values_are_keys``: there is no value projection; a head's value is its key as projected, before the rotation
+    (``value_dim`` == ``head_dim``).
+    ``names`` maps the roles q, k, v, o to tensor names below ``prefix``; when it also names q_bias or k_bias, that
+    projection adds the [out] bias of that name."""
 
     hidden_size: int
     num_heads: int
@@ -111,9 +123,14 @@ class CappedAttentionSpec:
     softcap: Optional[float] = None
     window: Optional[int] = None
     unit_norm_eps: Optional[float] = None
+    sink: bool = False
+    values_are_keys: bool = False
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
+
+    def has(self, role: str) -> bool:
+        return role in dict(self.names)
 
 
 @dataclass(frozen=True)
@@ -124,7 +141,14 @@ class LatentAttentionSpec:
     with a plain weight and ``norm_eps``) and ``rot_dim`` rotated key lanes shared by all heads (the last rows of
     the down projection).  A head's query is ``qk_dim`` plain lanes followed by ``rot_dim`` rotated lanes; its key
     is ``W_uk c`` followed by the shared rotated lanes; its value ``W_uv c`` (``v_dim`` lanes); the score is the
-    dot product times ``scale``; ordinary softmax over positions 0..p.  ``position`` rotates the ``rot_dim`` lanes.
+    dot product times ``scale``; ordinary softmax over positions 0..p, or with ``window`` w over the last w of them
+    (p itself included).  ``position`` rotates the ``rot_dim`` lanes.
+    ``q_rank`` not None: the queries go through a latent of their own, q = W_uq RMSnorm(W_dq h) (plain weight,
+    ``norm_eps``; roles dq, dq_norm, uq instead of q).  ``gated``: the concatenated heads are multiplied by
+    sigmoid(W_g h) before the output projection (role g).  ``own_kv`` False: the layer has no down projection and
+    reads the cache rows that another layer execution wrote (the plan's order says which), with its own
+    up-projections, queries and window; ``keep`` is then the window that the shared rows are kept for (None: all
+    of them), at least the window of every layer that reads them.
     ``names`` maps the roles q, dkv, dkv_norm, uk, uv, o to tensor names below ``prefix``."""
 
     hidden_size: int
@@ -138,9 +162,22 @@ class LatentAttentionSpec:
     position: object
     prefix: str
     names: Tuple[Tuple[str, str], ...]
+    q_rank: Optional[int] = None
+    window: Optional[int] = None
+    keep: Optional[int] = None      # positions the cache keeps; None with a window: the window itself
+    keeps_all: bool = False         # the cache keeps every position although this layer has a window (a reader has none)
+    gated: bool = False
+    own_kv: bool = True
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
+
+    @property
+    def cache_window(self) -> Optional[int]:
+        """How many positions the cache rows are kept for (None: all)."""
+        if self.keeps_all or self.window is None:
+            return None
+        return self.window if self.keep is None else max(self.keep, self.window)
 
 
 @dataclass(frozen=True)
@@ -234,6 +271,23 @@ class MLPSpec:
 
 
 @dataclass(frozen=True)
+class PolyNormMLPSpec:
+    """Dense feed-forward down(act(up x + b_up)) + b_down whose activation is a polynomial of row-normed powers:
+    act(z) = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(v) = v / sqrt(mean(v^2) + ``eps``) over a
+    token's ``intermediate_size`` values, (a, b, c, e) a stored tensor of four numbers.
+    ``names`` maps the roles up, up_bias, down, down_bias, act to tensor names below ``prefix``."""
+
+    hidden_size: int
+    intermediate_size: int
+    eps: float
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """Dense gated feed-forward: down(act(gate(x)) * up(x)), no biases."""
 
@@ -271,6 +325,23 @@ class SandwichBlockSpec:
 
 
 @dataclass(frozen=True)
+class ParallelBlockSpec:
+    """h = norm(x); x <- x + ``residual_mult`` * (mixer(h + conv(h)) + feed_forward(h)): one norm, both sublayers read
+    its output side by side.  conv is a causal convolution over time on each channel of h, ``conv_taps`` taps without
+    a bias (``conv_name``: [hidden, taps]), conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j), zeros before a sequence's
+    start; the last taps - 1 rows of h are part of a sequence's state.  ``conv_name`` None: the mixer reads h itself.
+    ``ffn`` None: the layer has no feed-forward.  The norm, the convolution's sum and the residual sum are fp32."""
+
+    norm: object
+    mixer: object
+    ffn: object
+    hidden_size: int
+    residual_mult: float = 1.0
+    conv_taps: int = 1
+    conv_name: Optional[str] = None
+
+
+@dataclass(frozen=True)
 class ReinjectSpec:
     """A step between layers that keeps no cache: h <- W [h ; e] + steps[index], with e the output of the
     embedding, W [hidden, 2 hidden] (the columns of h first) and ``steps`` [``num_steps``, hidden].  It opens a
@@ -299,11 +370,13 @@ class OrderEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """Token embedding: hidden[t] = table[token[t]], no scaling, nothing added."""
+    """Token embedding: hidden[t] = table[token[t]], no scaling, nothing added; with ``norm`` (a norm spec) the
+    rows then pass that norm, in fp32."""
 
     vocab_size: int
     hidden_size: int
     weight_name: str
+    norm: object = None
 
 
 @dataclass(frozen=True)

@@ -12,6 +12,7 @@
 // the softmax is the running-maximum form in fp32; the output accumulates in fp32.
 // Key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window).
 // With softcap c > 0 a score s (already times scale) becomes c tanh(s / c) before the softmax.
+// With sink = 1 the softmax has one more term, of score 0 and without a value: p_j = e^(s_j) / (1 + sum e^(s_k)).
 //
 // With splits > 1 every split writes an un-normalised partial (acc[d], max, sum) and
 // attention_combine merges them in split order.
@@ -55,7 +56,16 @@ struct AttnArgs {
   const int* page_ids;
   int n_seqs, nq, nkv, page_size, ring_pages, window, splits, bq, head_chunks;
   float scale, softcap;
+  int sink;             // 1: the softmax has one more term of score 0 and no value (one is added to its denominator)
 };
+
+// 1 / (l + e^-m) for sums l taken relative to the maximum m: the denominator with the sink's term, without overflow.
+__device__ __forceinline__ float sink_inverse(float m, float l) {
+  if (m == -INFINITY) return 0.f;
+  if (m >= 0.f) return 1.f / (l + expf(-m));
+  const float e = expf(m);
+  return e / fmaf(l, e, 1.f);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(NWARPS * 32)
@@ -224,7 +234,8 @@ attention_simt_kernel(AttnArgs a) {
     const int tok = q_begin + t0 + row / hpb;
     const int h = hk * g + chunk * 16 + row % hpb;
     if (a.splits == 1) {
-      const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+      float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+      if (a.sink) inv = sink_inverse(m[r], l[r]);
       T* o = (T*)a.out + ((size_t)tok * a.nq + h) * DV;
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
@@ -245,7 +256,7 @@ attention_simt_kernel(AttnArgs a) {
 
 // Merge the partials of one (token, head): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
 template <typename T>
-__global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int splits) {
+__global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int splits, int sink) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;  // token * nq + head
@@ -257,7 +268,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     const float ms = p[s * (DV + 2) + DV];
     if (ms != -INFINITY) denom += expf(ms - M) * p[s * (DV + 2) + DV + 1];
   }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  float inv = denom > 0.f ? 1.f / denom : 0.f;
+  if (sink) inv = sink_inverse(M, denom);
   for (int dd = threadIdx.x; dd < DV; dd += blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < splits; ++s) {
@@ -303,7 +315,7 @@ extern "C" int odi_attention_simt(const AttnArgs* args, int max_q_len, int n_tok
   if (rc != 0 || a.splits == 1) return rc;
   const int rows = n_tokens * a.nq;
   const int threads = DV >= 128 ? 128 : (DV >= 64 ? 64 : 32);
-  if (dtype == 0) odi_rc = launch_pdl((attention_combine_kernel<float>), dim3(rows), dim3(threads), 0, stream, a.partial, (float*)a.out, a.splits);
-  else odi_rc = launch_pdl((attention_combine_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, a.partial, (bf16*)a.out, a.splits);
+  if (dtype == 0) odi_rc = launch_pdl((attention_combine_kernel<float>), dim3(rows), dim3(threads), 0, stream, a.partial, (float*)a.out, a.splits, a.sink);
+  else odi_rc = launch_pdl((attention_combine_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, a.partial, (bf16*)a.out, a.splits, a.sink);
   return launch_status();
 }

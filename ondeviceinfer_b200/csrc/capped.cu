@@ -27,6 +27,7 @@ struct RotUnitArgs {
   int n_tokens, nq, nkv, d, dv, rot_dim, page_size, ring_pages, write_kv, unit;
   int d_store;          // lanes of a stored q or k head, >= d; the lanes beyond d are written as zero
   float eps;
+  int v_from_k;         // 1: there are no v lanes in `qkv`; the value of a head is its key as projected, before the rotation (dv == d)
 };
 
 // One warp per (token, head).  Lane i % 32 holds element i in register i / 32, so the partner of lane 2i
@@ -41,7 +42,7 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
   if (item >= (long)a.n_tokens * heads) return;
   const int t = (int)(item / heads), h = (int)(item % heads);
   const int d = a.d;
-  const size_t row = (size_t)(a.nq + a.nkv) * d + (size_t)a.nkv * a.dv;
+  const size_t row = (size_t)(a.nq + a.nkv) * d + (a.v_from_k ? (size_t)0 : (size_t)a.nkv * a.dv);
   const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);  // 0 q, 1 k, 2 v
   const int pos = a.tok_pos[t];
   const T* src;
@@ -58,7 +59,8 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
       src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + hk) * d;
       dst = (T*)a.k_pool + at * a.d_store;
     } else {
-      src = (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
+      src = a.v_from_k ? (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + hk) * d
+                       : (const T*)a.qkv + (size_t)t * row + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
       dst = (T*)a.v_pool + at * a.dv;
       for (int i = lane; i < a.dv; i += 32) dst[i] = src[i];
       return;
@@ -113,7 +115,7 @@ __global__ void rot_unit_prep_vec_kernel(RotUnitArgs a, int heads_per_warp) {
   if (item >= (long)a.n_tokens * groups) return;
   const int t = (int)(item / groups), h_begin = (int)(item % groups) * heads_per_warp;
   const int d = a.d, half = a.rot_dim >> 1;
-  const size_t row = (size_t)(a.nq + a.nkv) * d + (size_t)a.nkv * a.dv;
+  const size_t row = (size_t)(a.nq + a.nkv) * d + (a.v_from_k ? (size_t)0 : (size_t)a.nkv * a.dv);
   const bf16* base = (const bf16*)a.qkv + (size_t)t * row;
   const int pos = a.tok_pos[t];
   size_t at = 0;
@@ -126,7 +128,7 @@ __global__ void rot_unit_prep_vec_kernel(RotUnitArgs a, int heads_per_warp) {
     const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);
     if (kind == 2) {
       const int hk = h - a.nq - a.nkv;
-      const bf16* src = base + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
+      const bf16* src = a.v_from_k ? base + (size_t)(a.nq + hk) * d : base + (size_t)(a.nq + a.nkv) * d + (size_t)hk * a.dv;
       bf16* dst = (bf16*)a.v_pool + (at + (size_t)hk * a.page_size) * a.dv;
       for (int i = lane; i < a.dv; i += 32) dst[i] = src[i];
       continue;
@@ -181,8 +183,9 @@ __global__ void rot_unit_prep_vec_kernel(RotUnitArgs a, int heads_per_warp) {
 extern "C" int odi_rot_unit_prep(const RotUnitArgs* args, int dtype, cudaStream_t stream) {
   RotUnitArgs a = *args;
   if (a.n_tokens <= 0) return 0;
+  if (a.v_from_k && a.dv != a.d) return ODI_ERR_ARGUMENT;
   if (dtype == 1 && a.d == a.d_store && a.d % 4 == 0 && a.d <= 512 && a.d > 0 && a.dv > 0 && !(a.rot_dim & 1) && a.rot_dim <= a.d &&
-      ((uintptr_t)a.qkv | (uintptr_t)a.q_out | (uintptr_t)a.k_pool) % 8 == 0 && (a.nkv * a.dv) % 4 == 0) {
+      ((uintptr_t)a.qkv | (uintptr_t)a.q_out | (uintptr_t)a.k_pool) % 8 == 0 && (a.v_from_k || (a.nkv * a.dv) % 4 == 0)) {
     const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
     // few tokens: a warp per head for parallelism; many tokens: a warp takes a quarter of a token's heads
     const int hpw = a.n_tokens >= 256 ? (heads + 3) / 4 : 1;

@@ -472,7 +472,8 @@ extern "C" int odi_bias_add(void* y, const float* bias, long rows, int N, int dt
 // fp32 with the full-range sincosf.  One table serves every layer of the step.
 // ---------------------------------------------------------------------------------
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
-                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half,
+                                  float magnitude) {
   pdl_launch_dependents();
   pdl_wait();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -480,15 +481,15 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int*
   const int t = (int)(idx / half), i = (int)(idx % half);
   float sn, cs;
   sincosf((float)tok_pos[t] * inv_freq[i], &sn, &cs);
-  cos_t[idx] = cs;
-  sin_t[idx] = sn;
+  cos_t[idx] = cs * magnitude;
+  sin_t[idx] = sn * magnitude;
 }
 
 extern "C" int odi_rope_table(const float* inv_freq, const int* tok_pos, float* cos_t, float* sin_t, int n,
-                              int half, cudaStream_t stream) {
+                              int half, float magnitude, cudaStream_t stream) {
   if (n <= 0 || half <= 0) return 0;
   const long total = (long)n * half;
-  odi_rc = launch_pdl((rope_table_kernel), dim3((int)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, tok_pos, cos_t, sin_t, n, half);
+  odi_rc = launch_pdl((rope_table_kernel), dim3((int)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, tok_pos, cos_t, sin_t, n, half, magnitude);
   return launch_status();
 }
 

@@ -33,6 +33,9 @@ struct LatentPrepArgs {
   void* latent_out;      // null, or [n_tokens, R] in T: the normed latent once more, rows side by side
   void* key_rot_out;     // null, or [n_tokens, r] in T: the rotated shared key lanes once more
   int row;               // lanes of a cache row and of a head's absorbed query: R + r, or more (lanes beyond stay zero)
+  const void* down;      // null: the R + r lanes of the down projection follow the heads in `proj`; else
+  int ld_down;           // [n_tokens, ld_down] in T, the lanes at its start (queries that come from a product of their own)
+  int has_down;          // 0: a layer that reads another layer's cache rows: only the queries are prepared
 };
 
 __device__ __forceinline__ void rotated_pair(int lane, int rot_dims, int interleaved, int* a, int* b, int* i) {
@@ -60,24 +63,27 @@ latent_prep_kernel(LatentPrepArgs a) {
   const int t = blockIdx.x;
   const T* row = (const T*)a.proj + (size_t)t * a.ld;
   const int q_width = a.heads * (a.d + a.r);
-  const T* down = row + q_width;
+  const T* down = a.down != nullptr ? (const T*)a.down + (size_t)t * a.ld_down : row + q_width;
   const float* cs = a.cos_t + (size_t)t * (a.rot_dims / 2);
   const float* sn = a.sin_t + (size_t)t * (a.rot_dims / 2);
   const int W = a.row;
 
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < a.R; i += blockDim.x) { const float v = to_f<T>(down[i]); ss += v * v; }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / (float)a.R + a.eps);
+  float inv = 0.f;
+  if (a.has_down) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) { const float v = to_f<T>(down[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    inv = 1.0f / sqrtf(ss / (float)a.R + a.eps);
+  }
 
-  if (a.write_cache) {
+  if (a.has_down && a.write_cache) {
     const int seq = a.tok_seq[t], pos = a.tok_pos[t];
     const int page = a.page_ids[a.page_start[seq] + page_slot_of(pos, a.page_size, a.ring_pages)];
     T* dst = (T*)a.pool + ((size_t)page * a.page_size + (pos % a.page_size)) * W;
     for (int i = threadIdx.x; i < a.R; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(down[i]) * inv * a.norm_w[i]);
     for (int i = threadIdx.x; i < a.r; i += blockDim.x) dst[a.R + i] = from_f<T>(rotate_lane<T>(down + a.R, i, a, cs, sn));
   }
-  if (a.latent_out != nullptr) {
+  if (a.has_down && a.latent_out != nullptr) {
     T* lat = (T*)a.latent_out + (size_t)t * a.R;
     T* kr = (T*)a.key_rot_out + (size_t)t * a.r;
     for (int i = threadIdx.x; i < a.R; i += blockDim.x) lat[i] = from_f<T>(to_f<T>(down[i]) * inv * a.norm_w[i]);
@@ -148,7 +154,71 @@ extern "C" int odi_latent_prep(const LatentPrepArgs* args, int dtype, cudaStream
   const LatentPrepArgs a = *args;
   if (a.n_tokens <= 0) return 0;
   if (a.rot_dims % 2 != 0 || a.rot_dims > a.r || a.R <= 0 || a.heads <= 0 || a.row < a.R + a.r) return ODI_ERR_ARGUMENT;
+  if (!a.has_down && (a.write_cache || a.latent_out != nullptr)) return ODI_ERR_ARGUMENT;
   if (dtype == 0) odi_rc = launch_pdl((latent_prep_kernel<float>), dim3(a.n_tokens), dim3(128), 0, stream, a);
   else odi_rc = launch_pdl((latent_prep_kernel<bf16>), dim3(a.n_tokens), dim3(128), 0, stream, a);
+  return launch_status();
+}
+
+
+// ---------------------------------------------------------------------------------
+// A latent in front of a projection: out[t, :] = T(in[t, col .. col + Q) / sqrt(mean of squares + eps) * w),
+// the statistics and the scaling in fp32, one rounding.  `in` rows are ld lanes apart (the latent is a slice of a
+// wider product).
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+slice_norm_kernel(const T* __restrict__ in, const float* __restrict__ w, T* __restrict__ out, int ld, int col, int Q,
+                  float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const T* src = in + (size_t)blockIdx.x * ld + col;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < Q; i += blockDim.x) { const float v = to_f<T>(src[i]); ss += v * v; }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)Q + eps);
+  T* dst = out + (size_t)blockIdx.x * Q;
+  for (int i = threadIdx.x; i < Q; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(src[i]) * inv * w[i]);
+}
+
+extern "C" int odi_slice_norm(const void* in, const float* w, void* out, int rows, int ld, int col, int Q, float eps,
+                              int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (Q <= 0 || col < 0 || col + Q > ld) return ODI_ERR_ARGUMENT;
+  if (dtype == 0) odi_rc = launch_pdl((slice_norm_kernel<float>), dim3(rows), dim3(128), 0, stream, (const float*)in, w, (float*)out, ld, col, Q, eps);
+  else odi_rc = launch_pdl((slice_norm_kernel<bf16>), dim3(rows), dim3(128), 0, stream, (const bf16*)in, w, (bf16*)out, ld, col, Q, eps);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// An output gate on the heads: x[t, h, i] *= sigmoid(gate[t, col + h dv + i]) for i < dv; a head of x has `lanes`
+// lanes (>= dv; the ones beyond are left as they are), rows of `gate` are ld lanes apart.  The sigmoid and the
+// product in fp32, one rounding.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate, long total, int heads, int dv, int lanes,
+                                  int ld, int col) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int i = (int)(idx % dv);
+  const int h = (int)((idx / dv) % heads);
+  const long t = idx / ((long)dv * heads);
+  const float gv = to_f<T>(gate[t * ld + col + h * dv + i]);
+  T* p = x + (t * heads + h) * lanes + i;
+  *p = from_f<T>(to_f<T>(*p) / (1.0f + expf(-gv)));
+}
+
+extern "C" int odi_gate_heads(void* x, const void* gate, int rows, int heads, int dv, int lanes, int ld, int col,
+                              int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (heads <= 0 || dv <= 0 || lanes < dv || col < 0 || col + heads * dv > ld) return ODI_ERR_ARGUMENT;
+  const long total = (long)rows * heads * dv;
+  const long blocks = (total + 255) / 256;
+  if (blocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
+  if (dtype == 0) odi_rc = launch_pdl((gate_heads_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, total, heads, dv, lanes, ld, col);
+  else odi_rc = launch_pdl((gate_heads_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, total, heads, dv, lanes, ld, col);
   return launch_status();
 }

@@ -13,7 +13,7 @@ from typing import List, Optional
 
 import torch
 
-from ..cache import SequenceCache
+from ..cache import KVNeed, SequenceCache
 from ..config.specs import ModelPlan
 from ..parts import Runtime, build_part
 from ..parts.linear import flush_residual_add
@@ -40,8 +40,10 @@ class DecoderModel:
         self.keeps_embedding = any(getattr(layer, "reads_embedding", False) for layer in self.layers)
         for i, entry in enumerate(plan.order):
             if entry.cache_from is not None:
-                mine = self.layers[entry.layer].cache_needs()
-                theirs = self.layers[plan.order[entry.cache_from].layer].cache_needs()
+                # what is shared are the keys and values; fixed-size state is every execution's own
+                mine = tuple(n for n in self.layers[entry.layer].cache_needs() if isinstance(n, KVNeed))
+                theirs = tuple(n for n in self.layers[plan.order[entry.cache_from].layer].cache_needs()
+                               if isinstance(n, KVNeed))
                 if mine != theirs:
                     raise ValueError(f"order[{i}] reads the cache of entry {entry.cache_from}, whose layer keeps "
                                      f"{theirs}, but its own layer needs {mine}")
@@ -96,7 +98,8 @@ class DecoderModel:
 
     def make_cache(self, *, max_tokens: int, max_seqs: int, max_step_tokens: int = 256) -> SequenceCache:
         self._require_loaded()
-        needs = [self.layers[e.layer].cache_needs() if e.cache_from is None else () for e in self.plan.order]
+        needs = [tuple(n for n in self.layers[e.layer].cache_needs() if e.cache_from is None or not isinstance(n, KVNeed))
+                 for e in self.plan.order]
         return SequenceCache(needs, [e.cache_from for e in self.plan.order], dtype=self.runtime.dtype,
                              device=self.runtime.device, max_tokens=max_tokens, max_seqs=max_seqs,
                              max_step_tokens=max_step_tokens)

@@ -142,8 +142,9 @@ class _HeadPrepArgs(Structure):
                 ("page_size", c_int), ("ring_pages", c_int), ("write_kv", c_int), ("eps", c_float)]
 
 
-def rope_table(inv_freq: torch.Tensor, tok_pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor) -> None:
-    """cos_t/sin_t[t, i] = cos/sin(tok_pos[t] * inv_freq[i]) in fp32."""
+def rope_table(inv_freq: torch.Tensor, tok_pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
+               magnitude: float = 1.0) -> None:
+    """cos_t/sin_t[t, i] = magnitude * cos/sin(tok_pos[t] * inv_freq[i]) in fp32."""
     _require(inv_freq, "inv_freq", torch.float32, 1)
     _require(tok_pos, "tok_pos", torch.int32, 1)
     _require(cos_t, "cos_t", torch.float32, 2)
@@ -153,7 +154,7 @@ def rope_table(inv_freq: torch.Tensor, tok_pos: torch.Tensor, cos_t: torch.Tenso
         raise KernelError("rope tables must be [tokens, rot_dim / 2]")
     lib = load_library("elementwise")
     _check(lib.odi_rope_table(_ptr(inv_freq), _ptr(tok_pos), _ptr(cos_t), _ptr(sin_t), c_int(n), c_int(half),
-                              _stream()), "rope_table")
+                              c_float(magnitude), _stream()), "rope_table")
 
 
 def head_prep(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, cos_t, sin_t, tok_seq, tok_pos, page_start,
@@ -574,7 +575,7 @@ class _AttnArgs(Structure):
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("page_size", c_int),
                 ("ring_pages", c_int), ("window", c_int), ("splits", c_int), ("bq", c_int),
-                ("head_chunks", c_int), ("scale", c_float), ("softcap", c_float)]
+                ("head_chunks", c_int), ("scale", c_float), ("softcap", c_float), ("sink", c_int)]
 
 
 SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
@@ -583,9 +584,10 @@ SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
 def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                    nq: int, nkv: int, d: int, page_size: int, ring_pages: int, window: int, scale: float,
                    splits: int = 1, partial: Optional[torch.Tensor] = None, dv: Optional[int] = None,
-                   shared_kv: bool = False, softcap: float = 0.0) -> None:
+                   shared_kv: bool = False, softcap: float = 0.0, sink: bool = False) -> None:
     """Causal GQA over the paged cache for any mixture of prompt and decode sequences.  ``softcap`` c > 0:
-    scores (times ``scale``) become c tanh(score / c) before the softmax.
+    scores (times ``scale``) become c tanh(score / c) before the softmax.  ``sink``: the softmax has one more
+    term of score 0 and no value, p_j = exp(s_j) / (1 + sum_k exp(s_k)).
 
     ``dv`` (default ``d``): width of the value rows and of the output.  ``shared_kv``: a cached row is key and
     value at once (the value is its first ``dv`` lanes; ``v_pool`` is None), as in attention over a latent
@@ -614,7 +616,7 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _AttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                      _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, page_size, ring_pages, window, splits,
-                     0, 0, scale, softcap)
+                     0, 0, scale, softcap, 1 if sink else 0)
     defines = {"ODI_HEAD_DIM": d}
     if not plain:
         defines.update({"ODI_VALUE_DIM": dv, "ODI_SHARED_KV": 1 if shared_kv else 0})
@@ -893,26 +895,37 @@ class _LatentPrepArgs(Structure):
                 ("n_tokens", c_int), ("ld", c_int), ("heads", c_int), ("d", c_int), ("r", c_int), ("R", c_int),
                 ("rot_dims", c_int), ("interleaved", c_int), ("page_size", c_int), ("ring_pages", c_int),
                 ("write_cache", c_int), ("eps", c_float), ("latent_out", c_void_p), ("key_rot_out", c_void_p),
-                ("row", c_int)]
+                ("row", c_int), ("down", c_void_p), ("ld_down", c_int), ("has_down", c_int)]
 
 
 def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, norm_w: torch.Tensor, cos_t, sin_t,
                 tok_seq, tok_pos, page_start, page_ids, *, heads: int, d: int, r: int, R: int, rot_dims: int,
                 interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float,
                 latent_out: Optional[torch.Tensor] = None, key_rot_out: Optional[torch.Tensor] = None,
-                row: Optional[int] = None) -> None:
+                row: Optional[int] = None, down: Optional[torch.Tensor] = None, has_down: bool = True) -> None:
     """From the fused query / down projection ``proj`` [tokens, heads (d + r) + R + r]: the normed latent and the
     rotated shared key lanes into the token's cache row, each head's rotated query lanes into lanes R.. of
     ``q_abs`` [tokens, heads, row] (see ``csrc/latent.cu``).  ``row`` (default R + r) is the width of a cache row and
-    of a head's absorbed query; lanes beyond R + r are left as they are (zero)."""
+    of a head's absorbed query; lanes beyond R + r are left as they are (zero).  With ``down`` ([tokens, >= R + r],
+    the down projection in its first lanes) ``proj`` holds the queries only; ``has_down`` False (a layer that reads
+    another layer's cache rows) prepares the queries and nothing else."""
     row = R + r if row is None else row
     _require(proj, "proj", ndim=2)
     _require(q_abs, "q_abs", proj.dtype)
-    _require(pool, "pool", proj.dtype)
-    _require(norm_w, "norm_w", torch.float32, 1)
     n = proj.shape[0]
-    if (proj.shape[1] != heads * (d + r) + R + r or q_abs.numel() != n * heads * row or norm_w.numel() != R
-            or row < R + r or pool.shape[-1] != row):
+    apart = down is not None or not has_down
+    if has_down:
+        _require(pool, "pool", proj.dtype)
+        _require(norm_w, "norm_w", torch.float32, 1)
+        if norm_w.numel() != R or pool.shape[-1] != row:
+            raise KernelError("latent_prep sizes disagree")
+    elif write_cache or latent_out is not None:
+        raise KernelError("latent_prep without a down projection writes no cache rows")
+    if down is not None:
+        _require(down, "down", proj.dtype, 2)
+        if down.shape[0] != n or down.shape[1] < R + r:
+            raise KernelError("latent_prep: down is [tokens, >= R + r]")
+    if (proj.shape[1] != heads * (d + r) + (0 if apart else R + r) or q_abs.numel() != n * heads * row or row < R + r):
         raise KernelError("latent_prep sizes disagree")
     if rot_dims > 0:
         _require(cos_t, "cos_t", torch.float32, 2)
@@ -929,9 +942,37 @@ def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, nor
     args = _LatentPrepArgs(_ptr(proj), _ptr(q_abs), _ptr(pool), _ptr(norm_w), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                            _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, proj.shape[1], heads, d, r, R, rot_dims,
                            1 if interleaved else 0, page_size, ring_pages, 1 if write_cache else 0, eps,
-                           _ptr(latent_out), _ptr(key_rot_out), row)
+                           _ptr(latent_out), _ptr(key_rot_out), row, _ptr(down), 0 if down is None else down.shape[1],
+                           1 if has_down else 0)
     lib = load_library("latent")
     _check(lib.odi_latent_prep(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "latent_prep")
+
+
+def slice_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, col: int = 0) -> None:
+    """out[t] = cast(x[t, col : col + Q] / sqrt(mean of squares + eps) * weight), Q = len(weight): the RMS norm of a
+    slice of a wider product, statistics and scaling in fp32, one rounding."""
+    _require(x, "x", ndim=2)
+    _require(weight, "weight", torch.float32, 1)
+    _require(out, "out", x.dtype, 2)
+    Q = weight.numel()
+    if out.shape != (x.shape[0], Q) or col < 0 or col + Q > x.shape[1]:
+        raise KernelError(f"slice_norm sizes disagree: x {tuple(x.shape)}, col {col}, weight {Q}, out {tuple(out.shape)}")
+    lib = load_library("latent")
+    _check(lib.odi_slice_norm(_ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(col), c_int(Q),
+                              c_float(eps), c_int(dtype_code(x.dtype)), _stream()), "slice_norm")
+
+
+def gate_heads(x: torch.Tensor, gate: torch.Tensor, *, heads: int, dv: int, lanes: int, col: int = 0) -> None:
+    """x[t, h, i] *= sigmoid(gate[t, col + h dv + i]) for i < dv, in place; ``x`` is [tokens, heads * lanes]
+    (lanes >= dv; the lanes beyond stay), ``gate`` a product whose rows hold the gate's lanes from ``col`` on."""
+    _require(x, "x", ndim=2)
+    _require(gate, "gate", x.dtype, 2)
+    n = x.shape[0]
+    if x.shape[1] != heads * lanes or gate.shape[0] != n or lanes < dv or col < 0 or col + heads * dv > gate.shape[1]:
+        raise KernelError(f"gate_heads sizes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, heads={heads}, dv={dv}")
+    lib = load_library("latent")
+    _check(lib.odi_gate_heads(_ptr(x), _ptr(gate), c_int(n), c_int(heads), c_int(dv), c_int(lanes), c_int(gate.shape[1]),
+                              c_int(col), c_int(dtype_code(x.dtype)), _stream()), "gate_heads")
 
 
 class _LatentExpandArgs(Structure):
@@ -1150,22 +1191,25 @@ class _RotUnitArgs(Structure):
                 ("cos_t", c_void_p), ("sin_t", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p),
                 ("page_start", c_void_p), ("page_ids", c_void_p), ("n_tokens", c_int), ("nq", c_int), ("nkv", c_int),
                 ("d", c_int), ("dv", c_int), ("rot_dim", c_int), ("page_size", c_int), ("ring_pages", c_int),
-                ("write_kv", c_int), ("unit", c_int), ("d_store", c_int), ("eps", c_float)]
+                ("write_kv", c_int), ("unit", c_int), ("d_store", c_int), ("eps", c_float), ("v_from_k", c_int)]
 
 
 def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, page_start, page_ids, *, nq: int,
                   nkv: int, d: int, dv: int, rot_dim: int, page_size: int, ring_pages: int, write_kv: bool,
-                  unit_eps: Optional[float], d_store: Optional[int] = None) -> None:
+                  unit_eps: Optional[float], d_store: Optional[int] = None, v_from_k: bool = False) -> None:
     """Head preparation of an attention that rotates first and norms afterwards: q and k heads (``d`` lanes) of
     ``qkv`` [tokens, nq d + nkv d + nkv dv] are rotated over their first ``rot_dim`` lanes (lane 2i with 2i + 1;
     ``cos_t`` None: not at all) and, with ``unit_eps`` not None, divided by sqrt(mean of squares + eps); q goes to
     ``q_out``, k and the v heads (``dv`` lanes, as they are) to the token's row of their cache pages.  Stored q
-    and k heads have ``d_store`` >= ``d`` lanes (default ``d``), the ones beyond ``d`` zero."""
+    and k heads have ``d_store`` >= ``d`` lanes (default ``d``), the ones beyond ``d`` zero.  ``v_from_k``: ``qkv``
+    holds no v lanes ([tokens, nq d + nkv d]); the value of a head is its key as projected, before the rotation."""
     d_store = d if d_store is None else d_store
+    if v_from_k and dv != d:
+        raise KernelError("values that are the keys have the keys' width")
     _require(qkv, "qkv", ndim=2)
     _require(q_out, "q_out", qkv.dtype, 2)
     n = qkv.shape[0]
-    if qkv.shape[1] != (nq + nkv) * d + nkv * dv or q_out.shape != (n, nq * d_store):
+    if qkv.shape[1] != (nq + nkv) * d + (0 if v_from_k else nkv * dv) or q_out.shape != (n, nq * d_store):
         raise KernelError(f"rot_unit_prep sizes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, "
                           f"nq={nq}, nkv={nkv}, d={d}, dv={dv}")
     if write_kv:
@@ -1180,7 +1224,8 @@ def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, pa
             raise KernelError("rope tables must be [tokens, rot_dim / 2]")
     args = _RotUnitArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                         _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, nq, nkv, d, dv, rot_dim, page_size, ring_pages,
-                        1 if write_kv else 0, 0 if unit_eps is None else 1, d_store, 0.0 if unit_eps is None else unit_eps)
+                        1 if write_kv else 0, 0 if unit_eps is None else 1, d_store, 0.0 if unit_eps is None else unit_eps,
+                        1 if v_from_k else 0)
     lib = load_library("capped")
     _check(lib.odi_rot_unit_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "rot_unit_prep")
 
@@ -1427,3 +1472,81 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: in
     _check(lib.odi_sample(_ptr(logits), _ptr(out), c_int(n), c_int(V), c_int(V), c_float(temperature),
                           c_ulonglong(seed & ((1 << 64) - 1)), _ptr(streams), _ptr(steps), _ptr(advance_pos),
                           _ptr(advance_past), _ptr(active), _ptr(partials), _ptr(tickets), _stream()), "sample")
+
+
+
+# ------------------------------------------------------------------------------ parallel block, polynomial activation
+
+
+class _CanonArgs(Structure):
+    _fields_ = [("x", c_void_p), ("g", c_void_p), ("taps_w", c_void_p), ("state", c_void_p), ("tok_seq", c_void_p),
+                ("cu_q", c_void_p), ("slots", c_void_p), ("h_out", c_void_p), ("hc_out", c_void_p), ("n_tokens", c_int),
+                ("n_seqs", c_int), ("W", c_int), ("taps", c_int), ("eps", c_float)]
+
+
+CANON_MAX_TAPS = 8
+
+
+def _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, h_out, hc_out, eps) -> _CanonArgs:
+    _require(x, "x", torch.float32, 2)
+    _require(g, "g", torch.float32)
+    _require(taps_w, "taps_w", torch.float32, 2)
+    n, W = x.shape
+    taps = taps_w.shape[1]
+    if g.numel() != 1 or taps_w.shape[0] != W or not 1 <= taps <= CANON_MAX_TAPS:
+        raise KernelError(f"canon: one norm weight, taps [width, 1..{CANON_MAX_TAPS}] (got {tuple(g.shape)}, {tuple(taps_w.shape)})")
+    if taps > 1:
+        _require(state, "state", torch.float32, 3)
+        if state.shape[1:] != (taps - 1, W):
+            raise KernelError(f"canon: the state is [slots, taps - 1, width], not {tuple(state.shape)}")
+    for name, t in (("tok_seq", tok_seq), ("cu_q", cu_q), ("slots", slots)):
+        _require(t, name, torch.int32, 1)
+    return _CanonArgs(_ptr(x), _ptr(g), _ptr(taps_w), _ptr(state if taps > 1 else None), _ptr(tok_seq), _ptr(cu_q),
+                      _ptr(slots), _ptr(h_out), _ptr(hc_out), n, slots.numel(), W, taps, eps)
+
+
+def canon_norm(x, g, eps: float, taps_w, state, tok_seq, cu_q, slots, h_out, hc_out) -> None:
+    """h = x / sqrt(mean(x^2) + eps) * g (``g`` one number) per token into ``h_out``, and h + conv(h) into ``hc_out``
+    (both in the compute dtype), conv(h)_t = sum_j taps_w[:, j] h_(t - taps + 1 + j) over the sequence's earlier
+    tokens: those of this step, and before them ``state[slot]`` [taps - 1, width] (fp32: h of the sequence's last
+    positions, zero before its start).  The state is not changed: :func:`canon_state` moves it on afterwards."""
+    args = _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, h_out, hc_out, eps)
+    _require(h_out, "h_out", ndim=2)
+    _require(hc_out, "hc_out", h_out.dtype, 2)
+    if h_out.shape != x.shape or hc_out.shape != x.shape or tok_seq.numel() != x.shape[0]:
+        raise KernelError("canon_norm: outputs and tok_seq follow the tokens of x")
+    lib = load_library("parallel")
+    _check(lib.odi_canon_norm(byref(args), c_int(dtype_code(h_out.dtype)), _stream()), "canon_norm")
+
+
+def canon_state(x, g, eps: float, taps_w, state, tok_seq, cu_q, slots) -> None:
+    """After :func:`canon_norm` and before ``x`` changes: ``state[slot]`` becomes h of the last taps - 1 positions
+    of every sequence of the step (rows of the old state move up where a sequence brought fewer tokens)."""
+    if taps_w.shape[1] <= 1:
+        return
+    args = _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, None, None, eps)
+    lib = load_library("parallel")
+    _check(lib.odi_canon_state(byref(args), _stream()), "canon_state")
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps), (a, b, c, e) = ``coef``
+    (fp32); powers, means and the sum in fp32, one rounding."""
+    _require(z, "z", ndim=2)
+    _require(out, "out", z.dtype, 2)
+    _require(coef, "coef", torch.float32, 1)
+    if out.shape != z.shape or coef.numel() != 4:
+        raise KernelError(f"poly_norm sizes disagree: {tuple(z.shape)} -> {tuple(out.shape)}, coef {tuple(coef.shape)}")
+    lib = load_library("parallel")
+    _check(lib.odi_poly_norm(_ptr(z), _ptr(coef), _ptr(out), c_int(z.shape[0]), c_int(z.shape[1]), c_float(eps),
+                             c_int(dtype_code(z.dtype)), _stream()), "poly_norm")
+
+
+def scaled_add(x: torch.Tensor, y: torch.Tensor, m: float) -> None:
+    """x += m * y (fp32, in place)."""
+    _require(x, "x", torch.float32)
+    _require(y, "y", torch.float32)
+    if x.shape != y.shape:
+        raise KernelError(f"scaled_add sizes disagree: {tuple(x.shape)} and {tuple(y.shape)}")
+    lib = load_library("parallel")
+    _check(lib.odi_scaled_add(_ptr(x), _ptr(y), c_long(x.numel()), c_float(m), _stream()), "scaled_add")

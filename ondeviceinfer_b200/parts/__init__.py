@@ -7,11 +7,11 @@ from .channel_delta import ChannelDelta
 from .latent_attention import LatentAttention
 from .routed_experts import RoutedExperts
 from .embedding import OutputHead, TokenEmbedding
-from .block import PreNormBlock, Reinject, SandwichBlock
-from .mlp import GatedMLP, PlainMLP
+from .block import ParallelBlock, PreNormBlock, Reinject, SandwichBlock
+from .mlp import GatedMLP, PlainMLP, PolyNormMLP
 from .table_experts import TableExperts
 from .norm import RMSNorm
 from .position import NoPosition, Rotary
 
 __all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "gated_linear", "Attention", "PreNormBlock",
-           "GatedMLP", "PlainMLP", "SandwichBlock", "Reinject", "CappedAttention", "TableExperts", "LatentAttention", "ChannelDelta", "RoutedExperts", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]
+           "GatedMLP", "PlainMLP", "PolyNormMLP", "SandwichBlock", "ParallelBlock", "Reinject", "CappedAttention", "TableExperts", "LatentAttention", "ChannelDelta", "RoutedExperts", "RMSNorm", "NoPosition", "Rotary", "TokenEmbedding", "OutputHead"]

@@ -4,7 +4,8 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import PreNormBlockSpec, ReinjectSpec, SandwichBlockSpec
+from ..cache import StateNeed
+from ..config.specs import ParallelBlockSpec, PreNormBlockSpec, ReinjectSpec, SandwichBlockSpec
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
 
@@ -151,6 +152,79 @@ class SandwichBlock(Part):
         ctx.residual_sumsq = None
 
 
+class ParallelBlock(Part):
+    """h = norm(x); x += m (mixer(h + conv(h)) + feed_forward(h)): one norm whose output both sublayers read, a
+    short causal convolution over time in front of the mixer, one scaled add.
+
+    ``ops.canon_norm`` makes h and h + conv(h) in one pass over the stream (the norm's weight is one number);
+    the rows of h before a sequence's first token of the step come from the sequence's state, the fp32 h of its
+    last taps - 1 positions (a :class:`~ondeviceinfer_b200.cache.StateNeed` of the block, zero when a sequence
+    starts), which ``ops.canon_state`` moves on.  The mixer's fp32 output (a part that says ``returns_output``
+    returns it; any other adds into a zeroed buffer) takes the feed-forward's as its residual add, and
+    ``ops.scaled_add`` adds the sum to the stream."""
+
+    def __init__(self, spec: ParallelBlockSpec) -> None:
+        super().__init__(spec)
+        self.norm = build_part(spec.norm)
+        self.mixer = build_part(spec.mixer)
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        if not (getattr(spec.norm, "scalar_weight", False) and getattr(spec.norm, "scale_in_fp32", False)):
+            raise TypeError("this block's norm has one number as its weight and scales in fp32")
+        if spec.conv_taps < 1 or (spec.conv_name is None and spec.conv_taps != 1):
+            raise ValueError("conv_taps is at least 1, and 1 without a convolution")
+        self.taps = spec.conv_taps if spec.conv_name is not None else 1
+
+    def _children(self):
+        return tuple(part for part in (self.norm, self.mixer, self.ffn) if part is not None)
+
+    def tensor_decls(self):
+        decls = [d for part in self._children() for d in part.tensor_decls()]
+        if self.spec.conv_name is not None:
+            decls.append(TensorDecl(self.spec.conv_name, (self.spec.hidden_size, self.spec.conv_taps)))
+        return decls
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        for part in self._children():
+            part.load(fetch, runtime)
+        if self.spec.conv_name is not None:
+            self.taps_w = fetch.vector(self.spec.conv_name)
+        else:       # no convolution: one tap of zero, h + 0 h
+            self.taps_w = torch.zeros((self.spec.hidden_size, 1), dtype=torch.float32, device=runtime.device)
+
+    def _state_need(self):
+        return StateNeed((self.taps - 1, self.spec.hidden_size), torch.float32, "conv before the mixer")
+
+    def cache_needs(self):
+        needs = tuple(self.mixer.cache_needs())
+        return needs + ((self._state_need(),) if self.taps > 1 else ())
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self._children())
+
+    def forward(self, hidden, ctx, view) -> None:
+        ctx.defers_residual_add = False        # the parts' own products add (or return) at once
+        ctx.residual_sumsq = None
+        state = view.states[-1] if self.taps > 1 else None      # the block's need is the last one it names
+        n = hidden.shape[0]
+        h = torch.empty((n, self.spec.hidden_size), dtype=self.runtime.dtype, device=hidden.device)
+        hc = torch.empty_like(h)
+        eps = self.norm.spec.eps
+        from ..kernels import ops
+        ops.canon_norm(hidden, self.norm.scalar, eps, self.taps_w, state, ctx.tok_seq, ctx.cu_q, ctx.slots, h, hc)
+        ops.canon_state(hidden, self.norm.scalar, eps, self.taps_w, state, ctx.tok_seq, ctx.cu_q, ctx.slots)
+        if getattr(self.mixer, "returns_output", False):
+            branch = self.mixer.forward(hc, ctx, view, None)
+        else:
+            branch = torch.zeros_like(hidden)
+            self.mixer.forward(hc, ctx, view, branch)
+        if self.ffn is not None:
+            self.ffn.forward(h, ctx, branch)
+        ctx.residual_sumsq = None
+        ops.scaled_add(hidden, branch, self.spec.residual_mult)
+
+
 class Reinject(Part):
     """h <- W [h ; e] + steps[index], e the embedding's output (``ctx.embedded``): what opens a pass of a looped
     stack.  It keeps no cache and returns the new stream (the model goes on with what a layer returns)."""
@@ -182,4 +256,5 @@ class Reinject(Part):
 
 register_part(PreNormBlockSpec, PreNormBlock)
 register_part(SandwichBlockSpec, SandwichBlock)
+register_part(ParallelBlockSpec, ParallelBlock)
 register_part(ReinjectSpec, Reinject)

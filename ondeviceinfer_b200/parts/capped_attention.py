@@ -40,6 +40,8 @@ class CappedAttention(Part):
         self.lanes = -(-spec.head_dim // 4) * 4
         if spec.value_dim <= 0:
             raise ValueError("value_dim must be positive")
+        if spec.values_are_keys and spec.value_dim != spec.head_dim:
+            raise ValueError("values that are the keys have the keys' width")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("window must be positive")
         if spec.softcap is not None and spec.softcap <= 0:
@@ -53,16 +55,31 @@ class CappedAttention(Part):
     def tensor_decls(self):
         s = self.spec
         q, k, v = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
-        return [TensorDecl(s.name("q"), (q, s.hidden_size)), TensorDecl(s.name("k"), (k, s.hidden_size)),
-                TensorDecl(s.name("v"), (v, s.hidden_size)),
-                TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.value_dim))] + self.position.tensor_decls()
+        decls = [TensorDecl(s.name("q"), (q, s.hidden_size)), TensorDecl(s.name("k"), (k, s.hidden_size))]
+        if not s.values_are_keys:
+            decls.append(TensorDecl(s.name("v"), (v, s.hidden_size)))
+        decls.append(TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.value_dim)))
+        decls += [TensorDecl(s.name(role), (size,)) for role, size in (("q_bias", q), ("k_bias", k)) if s.has(role)]
+        return decls + self.position.tensor_decls()
 
     def load(self, fetch, runtime) -> None:
         s = self.spec
         self.runtime = runtime
-        # q, k and v rows concatenated: one product yields [tokens, nq d + nkv d + nkv dv]
-        self.w_qkv = torch.cat([fetch.matrix(s.name("q")), fetch.matrix(s.name("k")), fetch.matrix(s.name("v"))], 0)
+        # q, k and v rows concatenated: one product yields [tokens, nq d + nkv d + nkv dv] (no v rows when the
+        # values are the keys)
+        rows = [fetch.matrix(s.name("q")), fetch.matrix(s.name("k"))]
+        if not s.values_are_keys:
+            rows.append(fetch.matrix(s.name("v")))
+        self.w_qkv = torch.cat(rows, 0)
         self.w_o = fetch.matrix(s.name("o"))
+        # biases (fp32) concatenated like their weights; a projection without one adds zero
+        self.b_qkv = None
+        if s.has("q_bias") or s.has("k_bias"):
+            sizes = (("q_bias", s.num_heads * s.head_dim), ("k_bias", s.num_kv_heads * s.head_dim),
+                     ("v_bias", 0 if s.values_are_keys else s.num_kv_heads * s.value_dim))
+            self.b_qkv = torch.cat([fetch.vector(s.name(role)) if s.has(role)
+                                    else torch.zeros(size, dtype=torch.float32, device=runtime.device)
+                                    for role, size in sizes])
         self.position.load(fetch, runtime)
 
     def cache_needs(self):
@@ -80,10 +97,11 @@ class CappedAttention(Part):
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         q = torch.empty((n, s.num_heads * self.lanes), dtype=x.dtype, device=x.device)
-        ops.rot_unit_prep(linear(x, self.w_qkv), q, view.keys, view.values, cos, sin, ctx.tok_seq, ctx.tok_pos,
-                          page_start, page_ids, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, dv=s.value_dim,
-                          rot_dim=self.position.rot_dim, page_size=PAGE_SIZE, ring_pages=group.ring_pages,
-                          write_kv=view.writes_kv, unit_eps=s.unit_norm_eps, d_store=self.lanes)
+        ops.rot_unit_prep(linear(x, self.w_qkv, bias=self.b_qkv), q, view.keys, view.values, cos, sin, ctx.tok_seq,
+                          ctx.tok_pos, page_start, page_ids, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim,
+                          dv=s.value_dim, rot_dim=self.position.rot_dim, page_size=PAGE_SIZE, ring_pages=group.ring_pages,
+                          write_kv=view.writes_kv, unit_eps=s.unit_norm_eps, d_store=self.lanes,
+                          v_from_k=s.values_are_keys)
         o = self.attend(q, ctx, view, page_start, page_ids)
         if residual is None:
             return linear(o, self.w_o, out_dtype=torch.float32)
@@ -94,7 +112,7 @@ class CappedAttention(Part):
         """The attention output [tokens, heads * value_dim]."""
         s = self.spec
         o = torch.empty((ctx.n_tokens, s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
-        tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim)
+        tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim) and not s.sink
         common = dict(n_seqs=ctx.n_seqs, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim, page_size=PAGE_SIZE,
                       ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0)
         if (tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and self.lanes == s.value_dim
@@ -128,7 +146,7 @@ class CappedAttention(Part):
                                         splits=splits, partial=partial, **common)
             return o
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
-                           max_q_len=ctx.max_q_len, splits=splits, partial=partial, **common)
+                           max_q_len=ctx.max_q_len, splits=splits, partial=partial, sink=s.sink, **common)
         return o
 
 

@@ -17,25 +17,35 @@ import torch
 from ..config.specs import EmbeddingSpec, HeadSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
-from .base import Part, register_part
+from .base import Part, build_part, register_part
 from .linear import linear
 
 
 class TokenEmbedding(Part):
-    """hidden[t, :] = table[token[t], :], widened into the fp32 residual stream."""
+    """hidden[t, :] = table[token[t], :], widened into the fp32 residual stream; with a norm in the spec the rows
+    then pass it, in fp32 (a norm that scales in fp32)."""
 
     graph_safe = True
 
+    def __init__(self, spec) -> None:
+        super().__init__(spec)
+        self.norm = build_part(spec.norm) if getattr(spec, "norm", None) is not None else None
+
     def tensor_decls(self):
-        return [TensorDecl(self.spec.weight_name, (self.spec.vocab_size, self.spec.hidden_size))]
+        decls = [TensorDecl(self.spec.weight_name, (self.spec.vocab_size, self.spec.hidden_size))]
+        return decls + (self.norm.tensor_decls() if self.norm is not None else [])
 
     def load(self, fetch, runtime) -> None:
         self.runtime = runtime
         self.table = fetch.matrix(self.spec.weight_name)
+        if self.norm is not None:
+            self.norm.load(fetch, runtime)
 
     def forward(self, ctx) -> torch.Tensor:
         hidden = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=self.runtime.device)
         ops.embed(self.table, ctx.token_ids, hidden)
+        if self.norm is not None:
+            return self.norm(hidden, out_dtype=torch.float32)
         return hidden
 
 

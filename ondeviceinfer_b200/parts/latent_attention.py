@@ -20,7 +20,13 @@ products), laid out as heads of ``head_lanes`` lanes in pages of the step's own 
 prefill kernels for ordinary heads run on them; the output projection reads those padded heads through a copy
 of its weight with zero columns for the padding.  The cache still receives only the latent rows.
 
-Scores, softmax, the latent norm and the angles are fp32 in both compute dtypes.
+Options of the spec: queries through a latent of their own (its norm is ``ops.slice_norm`` on a slice of the first
+product, then a second product), a window (an argument of every attention kernel used; the cache is then a ring of
+pages), an output gate (``ops.gate_heads`` on the heads before the output projection), and a layer without a down
+projection that reads the rows another layer execution cached (in the whole-heads form it takes the step's latent
+rows from the step's context, where the layer that wrote them left them).
+
+Scores, softmax, the latent norms and the angles are fp32 in both compute dtypes.
 """
 
 from __future__ import annotations
@@ -40,6 +46,7 @@ WHOLE_HEADS_MAX_LANES = 256      # the widest head of the tensor-core prefill ke
 
 class LatentAttention(Part):
     graph_safe = True   # no host work that depends on the step's values
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
 
     def __init__(self, spec: LatentAttentionSpec) -> None:
         super().__init__(spec)
@@ -48,6 +55,10 @@ class LatentAttention(Part):
                 raise ValueError(f"{key} must be positive, got {getattr(spec, key)}")
         if spec.rot_dim < 0:
             raise ValueError("rot_dim must not be negative")
+        if spec.q_rank is not None and spec.q_rank <= 0:
+            raise ValueError("q_rank must be positive")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("window must be positive")
         self.position = build_part(spec.position)
         if self.position.rot_dim > spec.rot_dim:
             raise ValueError("the position encoding rotates more lanes than the heads have rotated lanes")
@@ -61,18 +72,38 @@ class LatentAttention(Part):
     def tensor_decls(self):
         s = self.spec
         q = s.num_heads * (s.qk_dim + s.rot_dim)
-        return [TensorDecl(s.name("q"), (q, s.hidden_size)),
-                TensorDecl(s.name("dkv"), (s.kv_rank + s.rot_dim, s.hidden_size)),
-                TensorDecl(s.name("dkv_norm"), (s.kv_rank,), "one_plus_normal"),
-                TensorDecl(s.name("uk"), (s.num_heads * s.qk_dim, s.kv_rank)),
-                TensorDecl(s.name("uv"), (s.num_heads * s.v_dim, s.kv_rank)),
-                TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.v_dim))] + self.position.tensor_decls()
+        if s.q_rank is None:
+            decls = [TensorDecl(s.name("q"), (q, s.hidden_size))]
+        else:
+            decls = [TensorDecl(s.name("dq"), (s.q_rank, s.hidden_size)),
+                     TensorDecl(s.name("dq_norm"), (s.q_rank,), "one_plus_normal"),
+                     TensorDecl(s.name("uq"), (q, s.q_rank))]
+        if s.own_kv:
+            decls += [TensorDecl(s.name("dkv"), (s.kv_rank + s.rot_dim, s.hidden_size)),
+                      TensorDecl(s.name("dkv_norm"), (s.kv_rank,), "one_plus_normal")]
+        decls += [TensorDecl(s.name("uk"), (s.num_heads * s.qk_dim, s.kv_rank)),
+                  TensorDecl(s.name("uv"), (s.num_heads * s.v_dim, s.kv_rank))]
+        if s.gated:
+            decls.append(TensorDecl(s.name("g"), (s.num_heads * s.v_dim, s.hidden_size)))
+        return decls + [TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.v_dim))] + self.position.tensor_decls()
 
     def load(self, fetch, runtime) -> None:
         s = self.spec
         self.runtime = runtime
-        self.w_in = torch.cat([fetch.matrix(s.name("q")), fetch.matrix(s.name("dkv"))], 0)
-        self.latent_norm = fetch.vector(s.name("dkv_norm"))
+        # One product for everything that reads the layer's input.  Queries without a latent of their own:
+        # [q | down projection] (the gate, if any, is a product of its own).  Queries through a latent:
+        # [down projection | query latent | gate], the down projection first so that its lanes start a row.
+        self.w_gate = self.w_uq = self.q_norm = None
+        down = [fetch.matrix(s.name("dkv"))] if s.own_kv else []
+        if s.q_rank is None:
+            self.w_in = torch.cat([fetch.matrix(s.name("q"))] + down, 0)
+            if s.gated:
+                self.w_gate = fetch.matrix(s.name("g"))
+        else:
+            self.w_in = torch.cat(down + [fetch.matrix(s.name("dq"))] + ([fetch.matrix(s.name("g"))] if s.gated else []), 0)
+            self.w_uq = fetch.matrix(s.name("uq"))
+            self.q_norm = fetch.vector(s.name("dq_norm"))
+        self.latent_norm = fetch.vector(s.name("dkv_norm")) if s.own_kv else None
         # per head: [kv_rank, qk_dim] so that q_plain W gives the query in latent lanes; [v_dim, kv_rank] as stored
         self.w_uk_t = fetch.matrix(s.name("uk")).view(s.num_heads, s.qk_dim, s.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = fetch.matrix(s.name("uv")).view(s.num_heads, s.v_dim, s.kv_rank).contiguous()
@@ -87,41 +118,72 @@ class LatentAttention(Part):
         self.position.load(fetch, runtime)
 
     def cache_needs(self):
-        return (KVNeed(1, self.row, None, value_plane=False),)
+        return (KVNeed(1, self.row, self.spec.cache_window, value_plane=False),)
 
-    def forward(self, x, ctx, view, residual) -> None:
+    def forward(self, x, ctx, view, residual):
+        """Adds the mixer's output to ``residual`` (fp32); with ``residual`` None returns it as a new fp32 tensor."""
         s = self.spec
         n = x.shape[0]
         group = view.kv_group
         page_start, page_ids = ctx.page_table(group.index)
         proj = linear(x, self.w_in)
+        gate, gate_col, down = None, 0, None
+        if s.q_rank is None:
+            queries = proj          # with the down projection behind the heads, if the layer has one
+            if s.gated:
+                gate = linear(x, self.w_gate)
+        else:
+            at = s.kv_rank + s.rot_dim if s.own_kv else 0
+            latent_q = torch.empty((n, s.q_rank), dtype=proj.dtype, device=proj.device)
+            ops.slice_norm(proj, self.q_norm, s.norm_eps, latent_q, col=at)
+            queries = linear(latent_q, self.w_uq)
+            down = proj if s.own_kv else None
+            gate, gate_col = (proj, at + s.q_rank) if s.gated else (None, 0)
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         q_abs = (torch.zeros if self.padded else torch.empty)((n, s.num_heads * self.row), dtype=proj.dtype,
                                                               device=proj.device)
-        whole_heads = (self.w_o_padded is not None and ctx.max_q_len >= WHOLE_HEADS_MIN_TOKENS
-                       and not any(ctx.past_lens) and not torch.cuda.is_current_stream_capturing())
-        latent = torch.empty((n, s.kv_rank), dtype=proj.dtype, device=proj.device) if whole_heads else None
-        key_rot = torch.empty((n, s.rot_dim), dtype=proj.dtype, device=proj.device) if whole_heads else None
-        ops.latent_prep(proj, q_abs, view.keys, self.latent_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start,
+        # a bfloat16 step whose sequences all start: whole heads for the tensor-core kernels, if this layer has the
+        # step's latent rows at hand (its own, or the ones that the layer whose cache it reads left on the context)
+        step_whole = (proj.dtype == torch.bfloat16 and ctx.max_q_len >= WHOLE_HEADS_MIN_TOKENS
+                      and not any(ctx.past_lens) and not torch.cuda.is_current_stream_capturing())
+        shared_key = ("latent rows of the step", view.keys.data_ptr())
+        latent = key_rot = None
+        if step_whole and s.own_kv:
+            latent = torch.empty((n, s.kv_rank), dtype=proj.dtype, device=proj.device)
+            key_rot = torch.empty((n, s.rot_dim), dtype=proj.dtype, device=proj.device)
+        ops.latent_prep(queries, q_abs, view.keys, self.latent_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start,
                         page_ids, heads=s.num_heads, d=s.qk_dim, r=s.rot_dim, R=s.kv_rank,
                         rot_dims=self.position.rot_dim if cos is not None else 0,
                         interleaved=getattr(self.position, "interleaved", False), page_size=PAGE_SIZE,
-                        ring_pages=group.ring_pages, write_cache=view.writes_kv, eps=s.norm_eps,
-                        latent_out=latent, key_rot_out=key_rot, row=self.row)
-        if whole_heads:
-            self._attend_whole_heads(proj, q_abs, latent, key_rot, ctx, residual)
-            return
-        ops.grouped_gemm_heads(proj, self.w_uk_t, q_abs, a_col=0, a_stride=s.qk_dim + s.rot_dim, c_col=0,
-                               c_stride=self.row, K=s.qk_dim)
-        latent_out = self.attend(q_abs, ctx, view, page_start, page_ids)
-        heads_out = torch.empty((n, s.num_heads * s.v_dim), dtype=proj.dtype, device=proj.device)
-        ops.grouped_gemm_heads(latent_out, self.w_uv, heads_out, a_col=0, a_stride=s.kv_rank, c_col=0,
-                               c_stride=s.v_dim, K=s.kv_rank)
-        linear(heads_out, self.w_o, residual=residual, track=ctx)
+                        ring_pages=group.ring_pages, write_cache=s.own_kv and view.writes_kv, eps=s.norm_eps,
+                        latent_out=latent, key_rot_out=key_rot, row=self.row, down=down, has_down=s.own_kv)
+        if step_whole:
+            if s.own_kv and view.writes_kv:
+                ctx.memo(shared_key, lambda: (latent, key_rot))
+            elif not s.own_kv:
+                latent, key_rot = ctx.memo(shared_key, lambda: (None, None))
+        if step_whole and self.w_o_padded is not None and latent is not None:
+            out, w_o = self._attend_whole_heads(queries, q_abs, latent, key_rot, ctx), self.w_o_padded
+            lanes = self.head_lanes
+        else:
+            ops.grouped_gemm_heads(queries, self.w_uk_t, q_abs, a_col=0, a_stride=s.qk_dim + s.rot_dim, c_col=0,
+                                   c_stride=self.row, K=s.qk_dim)
+            latent_out = self.attend(q_abs, ctx, view, page_start, page_ids)
+            out = torch.empty((n, s.num_heads * s.v_dim), dtype=proj.dtype, device=proj.device)
+            ops.grouped_gemm_heads(latent_out, self.w_uv, out, a_col=0, a_stride=s.kv_rank, c_col=0,
+                                   c_stride=s.v_dim, K=s.kv_rank)
+            w_o, lanes = self.w_o, s.v_dim
+        if s.gated:
+            ops.gate_heads(out, gate, heads=s.num_heads, dv=s.v_dim, lanes=lanes, col=gate_col)
+        if residual is None:
+            return linear(out, w_o, out_dtype=torch.float32)
+        linear(out, w_o, residual=residual, track=ctx)
+        return None
 
-    def _attend_whole_heads(self, proj, q_abs, latent, key_rot, ctx, residual) -> None:
-        """Prompts from their first token on: attention over up-projected heads in pages of the step's own."""
+    def _attend_whole_heads(self, proj, q_abs, latent, key_rot, ctx):
+        """Prompts from their first token on: attention over up-projected heads in pages of the step's own; returns
+        the padded heads [tokens, heads * head_lanes]."""
         s, n, lanes, dev = self.spec, proj.shape[0], self.head_lanes, proj.device
 
         def pages_of_the_step():
@@ -145,11 +207,16 @@ class LatentAttention(Part):
         out = torch.empty_like(q_full)
         sizes = dict(n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_heads, d=lanes,
                      page_size=PAGE_SIZE, scale=s.scale)
+        window = s.window or 0
         if lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS:
-            ops.attention_tcgen05(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, **sizes)
+            ops.attention_tcgen05(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, window=window,
+                                  ring_pages=0, **sizes)
+        elif window > 0:
+            ops.attention_capped(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, dv=lanes,
+                                 ring_pages=0, window=window, **sizes)
         else:
             ops.attention_mma(q_full, pools[0], pools[1], out, ctx.cu_q, no_past, page_start, page_ids, **sizes)
-        linear(out, self.w_o_padded, residual=residual, track=ctx)
+        return out
 
     def attend(self, q_abs, ctx, view, page_start, page_ids):
         """[tokens, heads * kv_rank]: per head the softmax-weighted sum of the latents it sees."""
@@ -159,13 +226,14 @@ class LatentAttention(Part):
         if ctx.max_q_len == 1:
             # single tokens: cut long key ranges so that enough blocks run side by side
             blocks = ctx.n_seqs * ((s.num_heads + 15) // 16)
-            splits = max(1, min(32, 592 // max(blocks, 1), (ctx.max_kv_len + 63) // 64))
+            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window)
+            splits = max(1, min(32, 592 // max(blocks, 1), (keys + 63) // 64))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.kv_rank + 2),), dtype=torch.float32,
                                       device=q_abs.device)
         ops.attention_simt(q_abs, view.keys, None, out, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
                            max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=1, d=self.row, dv=s.kv_rank, shared_kv=True,
-                           page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=0, scale=s.scale,
+                           page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale,
                            splits=splits, partial=partial)
         return out
 

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedMLPSpec, MLPSpec
+from ..config.specs import GatedMLPSpec, MLPSpec, PolyNormMLPSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
@@ -70,5 +70,40 @@ class PlainMLP(Part):
         return None
 
 
+class PolyNormMLP(Part):
+    """down(act(up x + b_up)) + b_down with act(z) = a N(z) + b N(z^2) + c N(z^3) + e, N the division of a token's
+    row of z by its root mean square.  The biases join their products' fp32 sums; the activation takes z in the
+    compute dtype, works in fp32 and rounds once (``csrc/parallel.cu``)."""
+
+    graph_safe = True
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
+
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(s.name("up"), (s.intermediate_size, s.hidden_size)),
+                TensorDecl(s.name("up_bias"), (s.intermediate_size,)),
+                TensorDecl(s.name("down"), (s.hidden_size, s.intermediate_size)),
+                TensorDecl(s.name("down_bias"), (s.hidden_size,)),
+                TensorDecl(s.name("act"), (4,), "one_plus_normal")]
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        self.w_up, self.b_up = fetch.matrix(s.name("up")), fetch.vector(s.name("up_bias"))
+        self.w_down, self.b_down = fetch.matrix(s.name("down")), fetch.vector(s.name("down_bias"))
+        self.coef = fetch.vector(s.name("act"))
+
+    def forward(self, x, ctx, residual):
+        """Adds to ``residual`` (fp32); with ``residual`` None returns the output as a new fp32 tensor."""
+        z = linear(x, self.w_up, bias=self.b_up)
+        act = torch.empty_like(z)
+        ops.poly_norm(z, self.coef, self.spec.eps, act)
+        if residual is None:
+            return linear(act, self.w_down, bias=self.b_down, out_dtype=torch.float32)
+        linear(act, self.w_down, bias=self.b_down, residual=residual)
+        return None
+
+
 register_part(GatedMLPSpec, GatedMLP)
+register_part(PolyNormMLPSpec, PolyNormMLP)
 register_part(MLPSpec, PlainMLP)

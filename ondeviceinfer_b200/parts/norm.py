@@ -25,7 +25,7 @@ class RMSNorm(Part):
             self.lazy = None      # the product prologue that norms rows itself rounds before it scales
 
     def tensor_decls(self):
-        return [TensorDecl(self.spec.weight_name, (self.spec.size,),
+        return [TensorDecl(self.spec.weight_name, () if self.spec.scalar_weight else (self.spec.size,),
                            "one_plus_normal" if self.spec.weight_offset == 0.0 else "normal")]
 
     def load(self, fetch, runtime) -> None:
@@ -33,6 +33,11 @@ class RMSNorm(Part):
         self.weight = fetch.vector(self.spec.weight_name)
         if self.spec.weight_offset != 0.0:
             self.weight = self.weight + self.spec.weight_offset
+        if self.spec.scalar_weight:
+            # one number for all coordinates: kept as it is for kernels that take it so, and laid out as a row
+            # for the norm kernels that take a weight per coordinate
+            self.scalar = self.weight.reshape(1).contiguous()
+            self.weight = self.scalar.expand(self.spec.size).contiguous()
 
     def lazy(self, x: torch.Tensor, parts: torch.Tensor):
         """The norm of the whole of ``x`` as a :class:`~ondeviceinfer_b200.parts.linear.NormedRows`:
@@ -40,11 +45,14 @@ class RMSNorm(Part):
         wrote ``x``.  For a consumer that says ``takes_lazy_norm``."""
         return NormedRows(x, self.weight, self.spec.eps, parts, self.runtime.dtype)
 
-    def __call__(self, x: torch.Tensor, rows=None, add=None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, rows=None, add=None, out_dtype=None) -> torch.Tensor:
         """``add`` (optional, without ``rows``): a product still to be added to ``x``; it is added in place in
-        the same pass when the kernel can, else beforehand."""
+        the same pass when the kernel can, else beforehand.  ``out_dtype`` (a norm with ``scale_in_fp32`` only):
+        float32 keeps the result in 32 bits whatever the compute dtype."""
         n = x.shape[0] if rows is None else rows.numel()
-        out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=x.device)
+        if out_dtype is not None and out_dtype != self.runtime.dtype and not self.spec.scale_in_fp32:
+            raise ValueError("only a norm that scales in fp32 gives its result in another dtype")
+        out = torch.empty((n, self.spec.size), dtype=out_dtype or self.runtime.dtype, device=x.device)
         if add is not None and (self.spec.scale_in_fp32 or
                                 not (rows is None and ops.rmsnorm_adds(x, self.weight, out, add))):
             ops.residual_add(x, add)

@@ -29,6 +29,25 @@ def scaled_frequencies(freqs, scaling):
     return out
 
 
+def ramped_frequencies(freqs, theta: float, dims: int, ramp):
+    """Frequencies slowed by a ramp over the pair index (``RotarySpec.index_ramp`` = factor, original, fast, slow),
+    and the number that cos and sin are multiplied by.  With n(t) = dims ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dims - 1), s_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
+    f_i <- s_i f_i / factor + (1 - s_i) f_i; magnitude = 0.1 ln(factor) + 1.  Host arithmetic in double."""
+    factor, original, fast, slow = (float(v) for v in ramp)
+
+    def pair_index(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_index(fast)), 0)
+    hi = min(math.ceil(pair_index(slow)), dims - 1)
+    out = []
+    for i, f in enumerate(freqs):
+        s = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(s * f / factor + (1.0 - s) * f)
+    return out, 0.1 * math.log(factor) + 1.0
+
+
 class Rotary(Part):
     """Rotary embedding (ondeviceinfer/layers.py:36-83); which lanes pair up (half-split or neighbours) is the
     mixer's business, the tables are the same.
@@ -51,6 +70,12 @@ class Rotary(Part):
         inv_freq = 1.0 / (self.spec.theta ** exponent)
         if self.spec.scaling is not None:
             inv_freq = torch.tensor(scaled_frequencies(inv_freq.double().tolist(), self.spec.scaling), dtype=torch.float32)
+        self.magnitude = 1.0
+        if self.spec.index_ramp is not None:
+            # in double from theta itself, not from the fp32 frequencies
+            exact = [float(self.spec.theta) ** (-2.0 * i / self.rot_dim) for i in range(self.rot_dim // 2)]
+            ramped, self.magnitude = ramped_frequencies(exact, float(self.spec.theta), self.rot_dim, self.spec.index_ramp)
+            inv_freq = torch.tensor(ramped, dtype=torch.float64).to(torch.float32)
         self.inv_freq = inv_freq.to(runtime.device)
 
     def rotary_tables(self, ctx):
@@ -58,7 +83,7 @@ class Rotary(Part):
             n, half = ctx.n_tokens, self.rot_dim // 2
             cos = torch.empty((n, half), dtype=torch.float32, device=self.inv_freq.device)
             sin = torch.empty_like(cos)
-            ops.rope_table(self.inv_freq, ctx.tok_pos, cos, sin)
+            ops.rope_table(self.inv_freq, ctx.tok_pos, cos, sin, self.magnitude)
             return cos, sin
 
         return ctx.memo(("rotary", self.spec), make)
