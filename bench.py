@@ -34,7 +34,7 @@ lengths and with temperature sampling.  One JSON line is printed:
 on the same configuration, and prints the same line with ``"impl": "reference"``.  Nothing of
 this library is imported in that arm.
 
-``--design lemesun`` (or ``nulalorn``) leaves the default workload alone and measures that architecture instead: prefill and
+``--design lemesun`` (or ``nulalorn``, ``zigivik``) leaves the default workload alone and measures that architecture instead: prefill and
 decode throughput at layer sizes like a real model's beside the dense model of equal width, one JSON line
 (``run_design_points``).
 
@@ -616,6 +616,27 @@ def _nulalorn_config(width, heads, kv_heads, dim, vdim, window, experts, top, ff
             "layers": [layer({"kind": "dense", "ff": dense_ff})] + [layer(moe) for _ in range(3)]}
 
 
+def _zigivik_config(width, heads, kv_heads, dim, latent_dim, rot, vdim, rank, q_rank, window, ff, vocab):
+    """Four layers: attention, latent attention, attention, latent attention on the rows of the second layer."""
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                           "rot": {"base": 10000.0, "dims": dim // 2}}}
+    mixer = {"heads": heads, "dim": latent_dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "q_rank": q_rank,
+             "scale": (latent_dim + rot) ** -0.5, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": mixer}
+    reader = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": dict(mixer, kv_from=1)}
+    return {"architecture": "Zigivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "canon": {"taps": 4}, "layers": [attention, latent, attention, reader]}
+
+
+ZIGIVIK_POINTS = {
+    "w2048": (_zigivik_config(2048, 16, 4, 128, 64, 64, 128, 512, 768, 1024, 5 * 1024, 32768),
+              _dense_config(2048, 16, 5 * 1024, 4, 32768)),
+    "w4096": (_zigivik_config(4096, 32, 8, 128, 64, 64, 128, 512, 1536, 1024, 12288, 32768),
+              _dense_config(4096, 32, 12288, 4, 32768)),
+}
+
 # name -> (the design's configuration, the dense model of equal width and equal active feed-forward width)
 NULALORN_POINTS = {
     "w2048": (_nulalorn_config(2048, 16, 4, 128, 128, 1024, 32, 4, 1024, 1024, 5 * 1024, 32768),
@@ -665,7 +686,7 @@ def _time_parts(model, cache, slots, runs, torch):
 
 
 def run_design_points(args) -> int:
-    """``--design lemesun|nulalorn``: prefill and decode throughput of that design at layer sizes like a real model's
+    """``--design lemesun|nulalorn|zigivik``: prefill and decode throughput of that design at layer sizes like a real model's
     (random weights), each beside the dense Qwen3 model of equal width, heads, layer executions and active
     feed-forward width, with the device time of every mixer and feed-forward call.  One JSON line; the default
     workload is untouched."""
@@ -683,7 +704,7 @@ def run_design_points(args) -> int:
     points = {}
     sampler = ClockSampler()
     sampler.start()
-    design_points = NULALORN_POINTS if args.design == "nulalorn" else DESIGN_POINTS
+    design_points = {"nulalorn": NULALORN_POINTS, "zigivik": ZIGIVIK_POINTS}.get(args.design, DESIGN_POINTS)
     for name, configs in design_points.items():
         if args.design_points and name not in args.design_points.split(","):
             continue
@@ -768,7 +789,7 @@ def main() -> int:
     parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
                         help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
     parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
-    parser.add_argument("--design", default=None, choices=["lemesun", "nulalorn"],
+    parser.add_argument("--design", default=None, choices=["lemesun", "nulalorn", "zigivik"],
                         help="instead of the default workload: this design at real layer sizes beside the dense model of equal size")
     parser.add_argument("--design-points", default=None, help="which of the design's sizes, with commas (default: all)")
     args = parser.parse_args()

@@ -7,7 +7,8 @@
 // works for any q_len >= 1 on top of any cached length, so prompts, their portions and single tokens all fit
 // (single tokens go to the second kernel of this file, which cuts the keys among blocks).
 //
-//   score = q . k * scale;  with softcap c > 0: score <- c tanh(score / c);
+//   score = q . k * scale;  with softcap c > 0: score <- c tanh(score / c);  with sink = 1 the softmax has one more
+//   term, of score 0 and without a value: p_j = e^(s_j) / (1 + sum_k e^(s_k));
 //   key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window).
 //
 // Key and value tiles (64 positions x D resp. DV bf16, contiguous in a page) are copied with cp.async, double
@@ -49,7 +50,17 @@ struct CappedAttnArgs {
   const int* page_ids;
   int n_seqs, nq, nkv, ring_pages, window;
   float scale, softcap;
+  int sink;               // 1: the softmax has one more term, of score 0 and without a value
 };
+
+// 1 / (l + 2^-m) for row sums l taken relative to the maximum m (log2 domain): the denominator with the sink's
+// term, without overflow; zero for a row that saw no key.
+__device__ __forceinline__ float sink_inverse_log2(float m, float l) {
+  if (m == -INFINITY) return 0.f;
+  if (m >= 0.f) return 1.f / (l + exp2f(-m));
+  const float e = exp2f(m);
+  return e / fmaf(l, e, 1.f);
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -227,7 +238,8 @@ attention_capped_kernel(CappedAttnArgs a) {
   // the row sums live spread over the 4 lanes of a quad
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+  float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+  if (a.sink) { inv_lo = sink_inverse_log2(m_lo, l_lo); inv_hi = sink_inverse_log2(m_hi, l_hi); }
   const int c = (lane & 3) * 2;
   if (r_lo < nt) {
     bf16* dst = a.out + ((size_t)(q_begin + t0 + r_lo) * a.nq + head) * DV;
@@ -404,7 +416,8 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
     }
     const int head = head0 + row;
     if (da.splits == 1) {
-      const float inv = L > 0.f ? 1.f / L : 0.f;
+      float inv = L > 0.f ? 1.f / L : 0.f;
+      if (a.sink) inv = sink_inverse_log2(M, L);
       bf16* dst = a.out + ((size_t)tok * a.nq + head) * DV;
       for (int dd = lane; dd < DV; dd += 32) {
         float v = 0.f;
@@ -427,7 +440,8 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
 }
 
 // Merge the partials of one (token, head): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, splits in order.
-__global__ void attention_capped_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
+__global__ void attention_capped_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits,
+                                                int sink) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int RS = DV + 2;
@@ -440,7 +454,8 @@ __global__ void attention_capped_combine_kernel(const float* __restrict__ partia
     const float ms = p[s * RS + DV];
     if (ms != -INFINITY) denom += expf(ms - M) * p[s * RS + DV + 1];
   }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  float inv = denom > 0.f ? 1.f / denom : 0.f;
+  if (sink) inv = sink_inverse_log2(M * LOG2E, denom);      // the partials' maxima are natural logarithms
   for (int dd = threadIdx.x; dd < DV; dd += blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < splits; ++s) {
@@ -477,7 +492,7 @@ extern "C" int odi_attention_capped_decode(const CappedAttnArgs* args, float* pa
   if (rc != 0 || splits == 1) return rc;
   const int rows = a.n_seqs * a.nq;
   const int threads = DV >= 128 ? 128 : (DV >= 64 ? 64 : 32);
-  odi_rc = launch_pdl(attention_capped_combine_kernel, dim3(rows), dim3(threads), 0, stream, (const float*)partial, a.out, splits);
+  odi_rc = launch_pdl(attention_capped_combine_kernel, dim3(rows), dim3(threads), 0, stream, (const float*)partial, a.out, splits, a.sink);
   return launch_status();
 }
 

@@ -89,6 +89,7 @@ struct TcAttnArgs {
   int window;             // > 0: the query at position p sees keys p - window + 1 .. p only
   int ring_pages;         // > 0: a sequence's page list is a ring: the page of position p is entry (p / 64) % ring_pages
   float softcap;          // c > 0: a score (times scale) becomes c tanh(score / c) before the softmax
+  int sink;               // 1: the softmax has one more term, of score 0 and without a value
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -480,7 +481,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const float sl2 = a.softcap > 0.f ? LOG2E : a.scale * LOG2E;
     const float two_over_cap = a.softcap > 0.f ? 2.f / a.softcap : 0.f;
     const int oldest = a.window > 0 ? pos - a.window + 1 : 0;
-    RowState st = {-INFINITY, 0.f};
+    // a sink is a key of score 0 and value 0 ahead of all others: the row starts from its maximum and its weight
+    RowState st = {a.sink ? 0.f : -INFINITY, a.sink ? 1.f : 0.f};
     bool ok = true;
     const uint32_t my_p_full = p_full + 16 * tile, my_pv_done = pv_done + 8 * tile;
     const uint32_t o_addr = tmem_base + lane_addr + O_COL(tile);

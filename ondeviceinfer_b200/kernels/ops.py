@@ -817,7 +817,7 @@ def attention_mma_combine(partial: torch.Tensor, out: torch.Tensor, past: torch.
 class _TcAttnArgs(Structure):
     _fields_ = [("out", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("status", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int),
-                ("scale", c_float), ("window", c_int), ("ring_pages", c_int), ("softcap", c_float)]
+                ("scale", c_float), ("window", c_int), ("ring_pages", c_int), ("softcap", c_float), ("sink", c_int)]
 
 
 TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
@@ -825,8 +825,9 @@ TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
 
 def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, heads_per_cta: int = 0, window: int = 0,
-                      ring_pages: int = 0, softcap: float = 0.0) -> None:
+                      ring_pages: int = 0, softcap: float = 0.0, sink: bool = False) -> None:
     """bf16 causal GQA for prefill on tcgen05: scores and outputs in tensor memory, TMA-fed pages.
+    ``sink``: one more term of score 0 and no value in the softmax.
     ``window`` > 0 keeps the last ``window`` keys visible (``ring_pages`` > 0: the page lists are rings);
     ``softcap`` c > 0 squashes the scores (times ``scale``) by c tanh(score / c).
     ``heads_per_cta``: 1, or 2 (two heads of a key/value group share a CTA and its K/V pages; needs an
@@ -842,7 +843,7 @@ def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, 
         raise KernelError("attention_tcgen05: q/out or the pools disagree")
     _, _, status = _gemm_buffers(q.device, 0)
     args = _TcAttnArgs(_ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start), _ptr(page_ids), _ptr(status),
-                       n_seqs, nq, nkv, scale, window, ring_pages, softcap)
+                       n_seqs, nq, nkv, scale, window, ring_pages, softcap, 1 if sink else 0)
     lib = load_library("attention_tcgen05", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), byref(args), c_int(n_tokens),
                                      c_int(max_q_len), c_long(k_pool.shape[0]), c_int(heads_per_cta), _stream()),
@@ -1233,7 +1234,8 @@ def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, pa
 class _CappedAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p), ("cu_q", c_void_p),
                 ("past", c_void_p), ("page_start", c_void_p), ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int),
-                ("nkv", c_int), ("ring_pages", c_int), ("window", c_int), ("scale", c_float), ("softcap", c_float)]
+                ("nkv", c_int), ("ring_pages", c_int), ("window", c_int), ("scale", c_float), ("softcap", c_float),
+                ("sink", c_int)]
 
 
 def attention_capped_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
@@ -1243,9 +1245,10 @@ def attention_capped_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
 
 def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int, nq: int,
                      nkv: int, d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
-                     softcap: float = 0.0) -> None:
+                     softcap: float = 0.0, sink: bool = False) -> None:
     """bf16 causal GQA on the tensor cores with squashed scores (``softcap`` c > 0: c tanh(score / c)), a window
-    (0: none; the cache may be a ring of pages) and value rows of ``dv`` lanes, for any mixture of sequences."""
+    (0: none; the cache may be a ring of pages) and value rows of ``dv`` lanes, for any mixture of sequences.
+    ``sink``: one more term of score 0 and no value in the softmax."""
     if not attention_capped_supported(q.dtype, d, dv) or page_size != 64:
         raise KernelError(f"attention_capped takes bfloat16 heads in steps of 16 up to 256 and pages of 64 (d={d}, dv={dv})")
     _require(q, "q", torch.bfloat16)
@@ -1256,14 +1259,15 @@ def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *
     if out.numel() != n_tokens * nq * dv or k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
         raise KernelError("attention_capped sizes disagree")
     args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
-                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap)
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0)
     lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
     _check(lib.odi_attention_capped(byref(args), c_int(max_q_len), _stream()), "attention_capped")
 
 
 def attention_capped_decode(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, nq: int, nkv: int,
                             d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
-                            softcap: float = 0.0, splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+                            softcap: float = 0.0, splits: int = 1, partial: Optional[torch.Tensor] = None,
+                            sink: bool = False) -> None:
     """:func:`attention_capped` for steps in which every sequence brings one token: each sequence's visible keys
     are cut into ``splits`` ranges that blocks of their own take; ``partial`` (fp32, tokens * nq * splits * (dv + 2))
     holds their results for the combine kernel."""
@@ -1280,7 +1284,7 @@ def attention_capped_decode(q, k_pool, v_pool, out, cu_q, past, page_start, page
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
-                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap)
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0)
     lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
     _check(lib.odi_attention_capped_decode(byref(args), _ptr(partial), c_int(splits), _stream()), "attention_capped_decode",
            2 if splits > 1 else 1)

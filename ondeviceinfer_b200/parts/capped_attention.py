@@ -112,16 +112,17 @@ class CappedAttention(Part):
         """The attention output [tokens, heads * value_dim]."""
         s = self.spec
         o = torch.empty((ctx.n_tokens, s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
-        tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim) and not s.sink
+        tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim)
         common = dict(n_seqs=ctx.n_seqs, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim, page_size=PAGE_SIZE,
-                      ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0)
+                      ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0,
+                      sink=s.sink)
         if (tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and self.lanes == s.value_dim
                 and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS):
             # bf16 prompts with heads of 64 or 128 lanes: scores and outputs in tensor memory (tcgen05)
             ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
                                   max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, page_size=PAGE_SIZE,
                                   scale=s.scale, window=s.window or 0, ring_pages=view.kv_group.ring_pages,
-                                  softcap=s.softcap or 0.0)
+                                  softcap=s.softcap or 0.0, sink=s.sink)
             return o
         if tensor_cores and ctx.max_q_len > 1:
             # other bf16 prompts and portions: the mma.sync form
@@ -146,7 +147,7 @@ class CappedAttention(Part):
                                         splits=splits, partial=partial, **common)
             return o
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
-                           max_q_len=ctx.max_q_len, splits=splits, partial=partial, sink=s.sink, **common)
+                           max_q_len=ctx.max_q_len, splits=splits, partial=partial, **common)
         return o
 
 
