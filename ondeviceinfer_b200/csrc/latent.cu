@@ -211,11 +211,41 @@ __global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate,
   *p = from_f<T>(to_f<T>(*p) / (1.0f + expf(-gv)));
 }
 
+// Eight bf16 lanes a thread (dv, lanes, ld and col multiples of 8, aligned tensors).
+__global__ void gate_heads_vec_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, long total8, int heads, int dv,
+                                      int lanes, int ld, int col) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per = dv >> 3;
+  const int i = (int)(idx % per) * 8;
+  const int h = (int)((idx / per) % heads);
+  const long t = idx / ((long)per * heads);
+  const uint4 graw = *(const uint4*)(gate + t * ld + col + h * dv + i);
+  bf16* p = x + (t * heads + h) * lanes + i;
+  uint4 xraw = *(const uint4*)p;
+  const __nv_bfloat162* g2 = (const __nv_bfloat162*)&graw;
+  __nv_bfloat162* x2 = (__nv_bfloat162*)&xraw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 g = __bfloat1622float2(g2[e]), v = __bfloat1622float2(x2[e]);
+    x2[e] = __floats2bfloat162_rn(v.x / (1.0f + expf(-g.x)), v.y / (1.0f + expf(-g.y)));
+  }
+  *(uint4*)p = xraw;
+}
+
 extern "C" int odi_gate_heads(void* x, const void* gate, int rows, int heads, int dv, int lanes, int ld, int col,
                               int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (heads <= 0 || dv <= 0 || lanes < dv || col < 0 || col + heads * dv > ld) return ODI_ERR_ARGUMENT;
   const long total = (long)rows * heads * dv;
+  if (dtype == 1 && dv % 8 == 0 && lanes % 8 == 0 && ld % 8 == 0 && col % 8 == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0) {
+    const long total8 = total / 8, vblocks = (total8 + 255) / 256;
+    if (vblocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
+    odi_rc = launch_pdl((gate_heads_vec_kernel), dim3((unsigned)vblocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, total8, heads, dv, lanes, ld, col);
+    return launch_status();
+  }
   const long blocks = (total + 255) / 256;
   if (blocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
   if (dtype == 0) odi_rc = launch_pdl((gate_heads_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, total, heads, dv, lanes, ld, col);

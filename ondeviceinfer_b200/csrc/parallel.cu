@@ -72,6 +72,110 @@ canon_norm_kernel(CanonArgs a) {
   }
 }
 
+// Sums of up to CANON_MAX_TAPS values over the block at once (one pair of barriers); every thread gets them.
+__device__ __forceinline__ void block_sum_taps(float* v, int count, float (*scratch)[33]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int k = 0; k < CANON_MAX_TAPS; ++k) if (k < count) v[k] = warp_sum(v[k]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < CANON_MAX_TAPS; ++k) if (k < count) scratch[k][warp] = v[k];
+  }
+  __syncthreads();
+  if (warp < count) {
+    float t = lane < nwarps ? scratch[warp][lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[warp][32] = t;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < CANON_MAX_TAPS; ++k) if (k < count) v[k] = scratch[k][32];
+}
+
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *(float4*)p = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+  uint2 packed;
+  *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(a, b);
+  *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(c, d);
+  *(uint2*)p = packed;
+}
+
+// The same for widths that are multiples of 4 (and blocks of at least as many warps as taps): 16-byte loads of the stream,
+// all rows' sums of squares in one reduction, 8- or 16-byte stores.  TAPS is the number of taps (a template argument
+// so that the rows' factors stay in registers).
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(256)
+canon_norm_vec_kernel(CanonArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[CANON_MAX_TAPS][33];
+  const int t = blockIdx.x;
+  const int seq = a.tok_seq[t];
+  const int i = t - a.cu_q[seq];
+  const int W = a.W, W4 = W >> 2;
+  const float g = a.g[0];
+  const float4* x4 = (const float4*)a.x;
+  float ss[CANON_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CANON_MAX_TAPS; ++k) ss[k] = 0.f;
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) {
+      if (i - k >= 0) {
+        const float4 v = x4[(size_t)(t - k) * W4 + c];
+        ss[k] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    }
+  }
+  block_sum_taps(ss, TAPS, scratch);
+  float inv[TAPS];
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) inv[k] = g / sqrtf(ss[k] / (float)W + a.eps);
+  const float4* st4 = a.state != nullptr ? (const float4*)(a.state + (size_t)a.slots[seq] * (TAPS - 1) * W) : nullptr;
+  T* h = (T*)a.h_out + (size_t)t * W;
+  T* hc = (T*)a.hc_out + (size_t)t * W;
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+    float4 v = x4[(size_t)t * W4 + c];
+    const float h0[4] = {v.x * inv[0], v.y * inv[0], v.z * inv[0], v.w * inv[0]};
+    float w[4][TAPS];
+    if (TAPS % 4 == 0) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; j += 4) {
+          const float4 q = *(const float4*)(a.taps_w + (size_t)(4 * c + e) * TAPS + j);
+          w[e][j] = q.x; w[e][j + 1] = q.y; w[e][j + 2] = q.z; w[e][j + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) w[e][j] = a.taps_w[(size_t)(4 * c + e) * TAPS + j];
+    }
+    float acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = h0[e] * w[e][TAPS - 1];
+#pragma unroll
+    for (int k = 1; k < TAPS; ++k) {
+      float4 r;
+      if (i - k >= 0) {
+        r = x4[(size_t)(t - k) * W4 + c];
+        r.x *= inv[k]; r.y *= inv[k]; r.z *= inv[k]; r.w *= inv[k];
+      } else {
+        r = st4[(size_t)(TAPS - 1 + i - k) * W4 + c];
+      }
+      acc[0] = fmaf(r.x, w[0][TAPS - 1 - k], acc[0]); acc[1] = fmaf(r.y, w[1][TAPS - 1 - k], acc[1]);
+      acc[2] = fmaf(r.z, w[2][TAPS - 1 - k], acc[2]); acc[3] = fmaf(r.w, w[3][TAPS - 1 - k], acc[3]);
+    }
+    store4<T>(h + 4 * c, h0[0], h0[1], h0[2], h0[3]);
+    store4<T>(hc + 4 * c, h0[0] + acc[0], h0[1] + acc[1], h0[2] + acc[2], h0[3] + acc[3]);
+  }
+}
+
 // One block per sequence: row j of the new state is h at index T - (taps - 1) + j of the step's tokens, or, for
 // a sequence that brought fewer than taps - 1 tokens, row T + j of the old state (ascending j, each channel by
 // one thread, so the move in place is safe).
@@ -100,11 +204,68 @@ canon_state_kernel(CanonArgs a) {
   }
 }
 
+// The same with 16-byte accesses and one reduction for all rows (widths that are multiples of 4).
+template <int TAPS>
+__global__ void __launch_bounds__(256)
+canon_state_vec_kernel(CanonArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[CANON_MAX_TAPS][33];
+  constexpr int keep = TAPS - 1;
+  const int seq = blockIdx.x;
+  const int W = a.W, W4 = W >> 2;
+  const int begin = a.cu_q[seq], T = a.cu_q[seq + 1] - begin;
+  const float g = a.g[0];
+  const float4* x4 = (const float4*)a.x;
+  float4* st4 = (float4*)(a.state + (size_t)a.slots[seq] * keep * W);
+  float ss[CANON_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CANON_MAX_TAPS; ++k) ss[k] = 0.f;
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < keep; ++j) {
+      const int i = T - keep + j;
+      if (i >= 0) {
+        const float4 v = x4[(size_t)(begin + i) * W4 + c];
+        ss[j] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    }
+  }
+  block_sum_taps(ss, keep, scratch);
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < keep; ++j) {
+      const int i = T - keep + j;
+      float4 v;
+      if (i >= 0) {
+        const float inv = g / sqrtf(ss[j] / (float)W + a.eps);
+        v = x4[(size_t)(begin + i) * W4 + c];
+        v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+      } else {
+        v = st4[(size_t)(T + j) * W4 + c];
+      }
+      st4[(size_t)j * W4 + c] = v;
+    }
+  }
+}
+
 extern "C" int odi_canon_norm(const CanonArgs* args, int dtype, cudaStream_t stream) {
   const CanonArgs a = *args;
   if (a.n_tokens <= 0) return 0;
   if (a.taps < 1 || a.taps > CANON_MAX_TAPS || a.W <= 0 || (a.taps > 1 && a.state == nullptr)) return ODI_ERR_UNSUPPORTED;
   const int threads = a.W >= 1024 ? 256 : 128;
+  const bool aligned = a.W % 4 == 0 && (((uintptr_t)a.x | (uintptr_t)a.state | (uintptr_t)a.h_out | (uintptr_t)a.hc_out |
+                                         (uintptr_t)a.taps_w) & 15) == 0;
+#define ODI_CANON(T, K) odi_rc = launch_pdl((canon_norm_vec_kernel<T, K>), dim3(a.n_tokens), dim3(threads), 0, stream, a)
+#define ODI_CANON_TAPS(T) switch (a.taps) { case 1: ODI_CANON(T, 1); break; case 2: ODI_CANON(T, 2); break; \
+    case 3: ODI_CANON(T, 3); break; case 4: ODI_CANON(T, 4); break; case 5: ODI_CANON(T, 5); break; \
+    case 6: ODI_CANON(T, 6); break; case 7: ODI_CANON(T, 7); break; default: ODI_CANON(T, 8); break; }
+  if (aligned && threads / 32 >= a.taps) {
+    if (dtype == 0) { ODI_CANON_TAPS(float) } else { ODI_CANON_TAPS(bf16) }
+    return launch_status();
+  }
+#undef ODI_CANON_TAPS
+#undef ODI_CANON
   if (dtype == 0) odi_rc = launch_pdl((canon_norm_kernel<float>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
   else odi_rc = launch_pdl((canon_norm_kernel<bf16>), dim3(a.n_tokens), dim3(threads), 0, stream, a);
   return launch_status();
@@ -114,7 +275,17 @@ extern "C" int odi_canon_state(const CanonArgs* args, cudaStream_t stream) {
   const CanonArgs a = *args;
   if (a.n_seqs <= 0 || a.taps <= 1) return 0;
   if (a.taps > CANON_MAX_TAPS || a.state == nullptr) return ODI_ERR_UNSUPPORTED;
-  odi_rc = launch_pdl((canon_state_kernel), dim3(a.n_seqs), dim3(a.W >= 1024 ? 256 : 128), 0, stream, a);
+  const int threads = a.W >= 1024 ? 256 : 128;
+  if (a.W % 4 == 0 && (((uintptr_t)a.x | (uintptr_t)a.state) & 15) == 0 && threads / 32 >= a.taps) {
+#define ODI_STATE(K) odi_rc = launch_pdl((canon_state_vec_kernel<K>), dim3(a.n_seqs), dim3(threads), 0, stream, a)
+    switch (a.taps) {
+      case 2: ODI_STATE(2); break; case 3: ODI_STATE(3); break; case 4: ODI_STATE(4); break; case 5: ODI_STATE(5); break;
+      case 6: ODI_STATE(6); break; case 7: ODI_STATE(7); break; default: ODI_STATE(8); break;
+    }
+#undef ODI_STATE
+    return launch_status();
+  }
+  odi_rc = launch_pdl((canon_state_kernel), dim3(a.n_seqs), dim3(threads), 0, stream, a);
   return launch_status();
 }
 
@@ -148,11 +319,73 @@ poly_norm_kernel(const T* __restrict__ z, const float* __restrict__ coef, T* __r
   }
 }
 
+// Eight lanes a step (F a multiple of 8, aligned rows): 16-byte loads of bf16, two of floats.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* v);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* v) {
+  const float4 lo = *(const float4*)p, hi = *(const float4*)(p + 4);
+  v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* v) {
+  const uint4 raw = *(const uint4*)p;
+  const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* v) {
+  *(float4*)p = make_float4(v[0], v[1], v[2], v[3]);
+  *(float4*)(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v) {
+  uint4 packed;
+  __nv_bfloat162* h2 = (__nv_bfloat162*)&packed;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  *(uint4*)p = packed;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_vec_kernel(const T* __restrict__ z, const float* __restrict__ coef, T* __restrict__ out, int F, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[CANON_MAX_TAPS][33];
+  const T* zr = z + (size_t)blockIdx.x * F;
+  float s[CANON_MAX_TAPS] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int i = threadIdx.x * 8; i < F; i += blockDim.x * 8) {
+    float v[8];
+    load8<T>(zr + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float v2 = v[e] * v[e], v3 = v2 * v[e];
+      s[0] += v2; s[1] += v2 * v2; s[2] += v3 * v3;
+    }
+  }
+  block_sum_taps(s, 3, scratch);
+  const float k1 = coef[0] / sqrtf(s[0] / (float)F + eps);
+  const float k2 = coef[1] / sqrtf(s[1] / (float)F + eps);
+  const float k3 = coef[2] / sqrtf(s[2] / (float)F + eps);
+  const float e0 = coef[3];
+  T* o = out + (size_t)blockIdx.x * F;
+  for (int i = threadIdx.x * 8; i < F; i += blockDim.x * 8) {
+    float v[8];
+    load8<T>(zr + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = fmaf(v[e], fmaf(v[e], fmaf(v[e], k3, k2), k1), e0);
+    store8<T>(o + i, v);
+  }
+}
+
 extern "C" int odi_poly_norm(const void* z, const float* coef, void* out, int rows, int F, float eps, int dtype,
                              cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F <= 0) return ODI_ERR_ARGUMENT;
   const int threads = F >= 2048 ? 256 : 128;
+  if (F % 8 == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0) {
+    if (dtype == 0) odi_rc = launch_pdl((poly_norm_vec_kernel<float>), dim3(rows), dim3(threads), 0, stream, (const float*)z, coef, (float*)out, F, eps);
+    else odi_rc = launch_pdl((poly_norm_vec_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, (const bf16*)z, coef, (bf16*)out, F, eps);
+    return launch_status();
+  }
   if (dtype == 0) odi_rc = launch_pdl((poly_norm_kernel<float>), dim3(rows), dim3(threads), 0, stream, (const float*)z, coef, (float*)out, F, eps);
   else odi_rc = launch_pdl((poly_norm_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, (const bf16*)z, coef, (bf16*)out, F, eps);
   return launch_status();
