@@ -165,6 +165,7 @@ ALL_SOURCES = {
     "latent": [{}],
     "capped": [{}],
     "attention_capped_mma": [{"ODI_HEAD_DIM": 128, "ODI_VALUE_DIM": 128}],
+    "attention_latent_mma": [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512}],      # a latent cache, on the tensor cores
     "grouped_gemm": [{}],
     "moe": [{}],
     "delta": [{"ODI_DELTA_DIM": d} for d in (64, 128)],

@@ -625,6 +625,48 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
                                   _stream()), "attention_simt", 2 if splits > 1 else 1)
 
 
+class _LatentAttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("pool", c_void_p), ("out", c_void_p), ("partial", c_void_p), ("cu_q", c_void_p),
+                ("past", c_void_p), ("page_start", c_void_p), ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int),
+                ("ring_pages", c_int), ("window", c_int), ("splits", c_int), ("bq", c_int), ("head_chunks", c_int),
+                ("scale", c_float)]
+
+
+def attention_latent_supported(dtype: torch.dtype, d: int, dv: int, page_size: int) -> bool:
+    """Whether :func:`attention_latent` takes these rows: bfloat16, rows in steps of 16 up to 1024 lanes, values in
+    steps of 16 up to 512 lanes and no wider than a row, pages of 64."""
+    return (dtype == torch.bfloat16 and page_size == 64 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 1024
+            and 16 <= dv <= min(d, 512))
+
+
+def attention_latent(q, pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int, nq: int, d: int,
+                     dv: int, page_size: int, ring_pages: int, window: int, scale: float, splits: int = 1,
+                     partial: Optional[torch.Tensor] = None) -> None:
+    """bf16 causal attention over shared rows on the tensor cores: a cached row of ``d`` lanes is the key of every
+    query head and its first ``dv`` lanes are the value, as in attention over a latent cache.  Any mixture of single
+    tokens and portions of prompts; ``window`` 0 for none (the cache may be a ring of pages); with ``splits`` > 1
+    each sequence's visible keys are cut into that many ranges and ``partial`` (fp32, tokens * nq * splits * (dv + 2))
+    holds their results for the combine kernel."""
+    if not attention_latent_supported(q.dtype, d, dv, page_size):
+        raise KernelError(f"attention_latent takes bfloat16 rows in steps of 16 up to 1024, values up to 512 and pages "
+                          f"of 64 (d={d}, dv={dv}, page_size={page_size})")
+    _require(q, "q", torch.bfloat16)
+    _require(out, "out", torch.bfloat16)
+    _require(pool, "pool", torch.bfloat16)
+    n_tokens = q.numel() // (nq * d)
+    if out.numel() != n_tokens * nq * dv or pool.shape[-1] != d:
+        raise KernelError("attention_latent sizes disagree")
+    if splits > 1:
+        need = n_tokens * nq * splits * (dv + 2)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
+    args = _LatentAttnArgs(_ptr(q), _ptr(pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past), _ptr(page_start),
+                           _ptr(page_ids), n_seqs, nq, ring_pages, window, splits, 0, 0, scale)
+    lib = load_library("attention_latent_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
+    _check(lib.odi_attention_latent_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(page_size), _stream()),
+           "attention_latent", 2 if splits > 1 else 1)
+
+
 class _MmaAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),

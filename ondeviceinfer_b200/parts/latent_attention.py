@@ -10,8 +10,9 @@ up-projection is applied to the attention's output.  Steps of ``forward``:
 1. one product for the query and the down projection;
 2. head preparation (``csrc/latent.cu``): latent norm, rotation, cache write, rotated query lanes;
 3. a product per head that folds ``W_uk`` into the plain query lanes (``csrc/grouped_gemm.cu``);
-4. attention over the cache pages (``csrc/attention_simt.cu`` built for shared rows), split over the keys
-   for single-token steps;
+4. attention over the cache pages, split over the keys for single-token steps: on the tensor cores
+   (``csrc/attention_latent_mma.cu``) for bfloat16 rows in steps of 16 lanes, else ``csrc/attention_simt.cu`` built
+   for shared rows;
 5. a product per head with ``W_uv``, then the output projection with the residual add.
 
 A bfloat16 step whose sequences all start (prompts) takes the other way round instead, because whole heads are
@@ -62,9 +63,11 @@ class LatentAttention(Part):
         self.position = build_part(spec.position)
         if self.position.rot_dim > spec.rot_dim:
             raise ValueError("the position encoding rotates more lanes than the heads have rotated lanes")
-        # width of a cache row and of an absorbed query: the attention kernel reads rows four lanes at a time, so
-        # the lanes are rounded up and the ones beyond kv_rank + rot_dim stay zero in the cache and in the query
-        self.row = -(-(spec.kv_rank + spec.rot_dim) // 4) * 4
+        # width of a cache row and of an absorbed query: the attention kernels read rows 16 lanes at a time on the
+        # tensor cores (which take latents in steps of 16) and four at a time otherwise, so the lanes are rounded up
+        # and the ones beyond kv_rank + rot_dim stay zero in the cache and in the query
+        step = 16 if spec.kv_rank % 16 == 0 else 4
+        self.row = -(-(spec.kv_rank + spec.rot_dim) // step) * step
         self.padded = self.row != spec.kv_rank + spec.rot_dim
         # lanes of a whole head (query/key: plain + rotated; value), in the steps of 16 the prefill kernels take
         self.head_lanes = -(-max(spec.qk_dim + spec.rot_dim, spec.v_dim) // 16) * 16
@@ -222,15 +225,24 @@ class LatentAttention(Part):
         """[tokens, heads * kv_rank]: per head the softmax-weighted sum of the latents it sees."""
         s = self.spec
         out = torch.empty((ctx.n_tokens, s.num_heads * s.kv_rank), dtype=q_abs.dtype, device=q_abs.device)
+        tensor_cores = ops.attention_latent_supported(q_abs.dtype, self.row, s.kv_rank, PAGE_SIZE)
         splits, partial = 1, None
         if ctx.max_q_len == 1:
-            # single tokens: cut long key ranges so that enough blocks run side by side
+            # single tokens: cut long key ranges so that enough blocks run side by side (a block of the tensor-core
+            # kernel fills a multiprocessor; two of the other kernel's fit)
             blocks = ctx.n_seqs * ((s.num_heads + 15) // 16)
-            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window)
-            splits = max(1, min(32, 592 // max(blocks, 1), (keys + 63) // 64))
+            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window + PAGE_SIZE)
+            room = 148 if tensor_cores else 592
+            splits = max(1, min(32, room // max(blocks, 1), (keys + 63) // 64))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.kv_rank + 2),), dtype=torch.float32,
                                       device=q_abs.device)
+        if tensor_cores:
+            ops.attention_latent(q_abs, view.keys, out, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
+                                 max_q_len=ctx.max_q_len, nq=s.num_heads, d=self.row, dv=s.kv_rank, page_size=PAGE_SIZE,
+                                 ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, splits=splits,
+                                 partial=partial)
+            return out
         ops.attention_simt(q_abs, view.keys, None, out, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
                            max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=1, d=self.row, dv=s.kv_rank, shared_kv=True,
                            page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale,

@@ -279,6 +279,53 @@ def test_softmax_with_a_sink_on_the_tensor_cores(d, window, T, past, splits):
         assert (got - want).abs().max() < 3e-2, kind
 
 
+def _shared_row_reference(q, rows, dv, scale, window, past):
+    """Ordinary softmax where a cached row is every head's key and its first ``dv`` lanes are the value."""
+    T, nq, _ = q.shape
+    i = past + torch.arange(T)[:, None]
+    j = torch.arange(rows.shape[0])[None, :]
+    see = (j <= i) & ((i - j) < window if window else True)
+    out = torch.zeros(T, nq, dv, dtype=torch.float64)
+    for h in range(nq):
+        s = (q[:, h].double() @ rows.double().T * scale).masked_fill(~see, -math.inf)
+        out[:, h] = torch.softmax(s, -1) @ rows[:, :dv].double()
+    return out
+
+
+@pytest.mark.parametrize("window,T,past,splits", [(None, 150, 0, 1), (64, 150, 0, 1), (65, 70, 130, 1), (1, 20, 50, 1),
+                                                   (None, 1, 0, 1), (7, 1, 190, 3), (None, 1, 700, 5), (300, 1, 700, 4),
+                                                   (128, 1, 127, 2), (128, 1, 128, 2), (None, 3, 447, 1)])
+@pytest.mark.parametrize("d,dv,nq", [(32, 16, 1), (48, 32, 3), (96, 80, 16), (576, 512, 20)])
+def test_shared_row_attention_on_the_tensor_cores(d, dv, nq, window, T, past, splits):
+    """The bfloat16 kernel over a latent cache: prompts' portions and single tokens with split keys, head counts
+    below, at and above a block's sixteen rows.  One head asks sharply for the oldest key it may see and another for
+    the one just outside its window, so a window that is one off, or a split that loses its range, shows."""
+    g = torch.Generator().manual_seed(T + past + d + nq)
+    total, scale = past + T, 1.0 / math.sqrt(d)
+    rows = torch.randn(total, d, generator=g)
+    q = torch.randn(T, nq, d, generator=g)
+    for t in range(T):
+        p = past + t
+        oldest = max(0, p - window + 1) if window else 0
+        q[t, 0] = 20.0 * rows[oldest] / scale / rows[oldest].square().sum()
+        if nq > 1 and oldest > 0:
+            q[t, 1] = 20.0 * rows[oldest - 1] / scale / rows[oldest - 1].square().sum()
+    q, rows = q.bfloat16(), rows.bfloat16()
+    want = _shared_row_reference(q, rows, dv, scale, window, past)
+    n_pages = -(-total // 64)
+    pool = _paged(rows[:, None], n_pages).reshape(n_pages, 64, d).cuda()
+    out = torch.empty((T, nq * dv), dtype=torch.bfloat16, device="cuda")
+    partial = torch.empty(T * nq * splits * (dv + 2), device="cuda") if splits > 1 else None
+    ops.attention_latent(q.reshape(T, -1).cuda(), pool, out, ints(0, T), ints(past), ints(0, n_pages),
+                         torch.arange(n_pages, dtype=torch.int32, device="cuda"), n_seqs=1, max_q_len=T, nq=nq, d=d, dv=dv,
+                         page_size=64, ring_pages=0, window=window or 0, scale=scale, splits=splits, partial=partial)
+    got = out.view(T, nq, dv).cpu().double()
+    assert (got - want).abs().max() < 3e-2
+    # the sharp head's output is (nearly) the row it asked for
+    oldest = max(0, past + T - 1 - window + 1) if window else 0
+    assert (got[-1, 0] - rows[oldest, :dv].double()).abs().max() < 6e-2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_rotary_tables_with_a_frequency_ramp(dtype, tmp_path_factory):
     model = engine("A", dtype, tmp_path_factory)
