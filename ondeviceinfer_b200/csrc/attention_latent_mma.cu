@@ -315,31 +315,38 @@ attention_latent_mma_kernel(LatentAttnArgs a) {
   }
 }
 
-// Merge the partials of one (token, head): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
+// Merge the partials of one (token, head): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.  The first warp
+// turns the splits' maxima and sums into one weight per split (at most 32 splits); then every thread adds up its lanes.
 __global__ void attention_latent_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float weight[32];
   const size_t row = blockIdx.x;  // token * nq + head
   const float* p = partial + row * splits * (DV + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (DV + 2) + DV]);
-  float denom = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = p[s * (DV + 2) + DV];
-    if (ms != -INFINITY) denom += expf(ms - M) * p[s * (DV + 2) + DV + 1];
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float ms = s < splits ? p[s * (DV + 2) + DV] : -INFINITY;
+    const float ls = s < splits ? p[s * (DV + 2) + DV + 1] : 0.f;
+    float M = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float e = ms == -INFINITY ? 0.f : expf(ms - M);
+    float denom = e * ls;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    weight[s] = denom > 0.f ? e / denom : 0.f;
   }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  __syncthreads();
   for (int dd = threadIdx.x * 2; dd < DV; dd += blockDim.x * 2) {
     float v0 = 0.f, v1 = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
-      const float ms = p[s * (DV + 2) + DV];
-      if (ms != -INFINITY) {
-        const float w = expf(ms - M);
-        const float2 x = *(const float2*)(p + s * (DV + 2) + dd);
-        v0 += w * x.x; v1 += w * x.y;
-      }
+      const float w = weight[s];
+      const float2 x = *(const float2*)(p + s * (DV + 2) + dd);
+      // a split without a visible key has weight zero, and zeros as its sums
+      v0 = fmaf(w, x.x, v0); v1 = fmaf(w, x.y, v1);
     }
-    *(uint32_t*)(out + row * DV + dd) = pack_bf16(v0 * inv, v1 * inv);
+    *(uint32_t*)(out + row * DV + dd) = pack_bf16(v0, v1);
   }
 }
 
@@ -350,7 +357,7 @@ extern "C" int odi_attention_latent_mma(const LatentAttnArgs* args, int max_q_le
                                         cudaStream_t stream) {
   LatentAttnArgs a = *args;
   if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (page_size != PAGE || a.splits < 1 || a.n_seqs > 65535 || a.nq < 1) return ODI_ERR_UNSUPPORTED;
+  if (page_size != PAGE || a.splits < 1 || a.splits > 32 || a.n_seqs > 65535 || a.nq < 1) return ODI_ERR_UNSUPPORTED;
   if (a.splits > 1 && a.partial == nullptr) return ODI_ERR_ARGUMENT;
   const int hpb = a.nq < 16 ? a.nq : 16;
   a.head_chunks = (a.nq + 15) / 16;
@@ -368,7 +375,7 @@ extern "C" int odi_attention_latent_mma(const LatentAttnArgs* args, int max_q_le
   odi_rc = launch_pdl(attention_latent_mma_kernel, grid, dim3(WARPS * 32), (size_t)SMEM_BYTES, stream, a);
   const int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;
-  const int threads = DV >= 256 ? 128 : (DV >= 128 ? 64 : 32);
+  const int threads = DV >= 512 ? 256 : (DV >= 256 ? 128 : (DV >= 128 ? 64 : 32));
   odi_rc = launch_pdl(attention_latent_combine_kernel, dim3(n_tokens * a.nq), dim3(threads), 0, stream,
                       (const float*)a.partial, a.out, a.splits);
   return launch_status();

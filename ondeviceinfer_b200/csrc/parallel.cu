@@ -7,7 +7,10 @@
 //    h + conv(h) in T for the mixer, conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j).  The rows before t come from
 //    the step's own tokens (their norm is taken again: the rows are in L2) or, before the first token that a
 //    sequence brings, from the sequence's state: h of its last taps - 1 positions, fp32, zero before its start.
-//  * canon_state: afterwards, the state of every sequence moved on by the tokens it brought.
+//    A sequence that brings one token has its state moved on in the same launch (the thread that reads a channel's
+//    state rows writes them back shifted).  For many tokens a block takes a run of them, so that a row's norm is
+//    taken once per run instead of once per tap.
+//  * canon_state: afterwards, the state of every sequence that brought more than one token moved on by them.
 //  * poly_norm: out = a N(z) + b N(z^2) + c N(z^3) + e, N(v) = v / sqrt(mean(v^2) + eps) over a token's row.
 //  * scaled_add: x += m y on fp32 rows.
 // Norms, the convolution's sum and the powers are fp32 in both compute dtypes; each output is rounded once.
@@ -53,6 +56,7 @@ canon_norm_kernel(CanonArgs a) {
     }
   }
   const float* st = a.state != nullptr ? a.state + (size_t)a.slots[seq] * (taps - 1) * W : nullptr;
+  const bool single = st != nullptr && a.cu_q[seq + 1] - a.cu_q[seq] == 1;
   T* h = (T*)a.h_out + (size_t)t * W;
   T* hc = (T*)a.hc_out + (size_t)t * W;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
@@ -69,6 +73,11 @@ canon_norm_kernel(CanonArgs a) {
     }
     h[c] = from_f<T>(h0);
     hc[c] = from_f<T>(h0 + acc);
+    if (single) {      // a sequence of one token: its state moves on here (this thread alone touches the channel)
+      float* sw = a.state + (size_t)a.slots[seq] * (taps - 1) * W;
+      for (int j = 0; j + 2 < taps; ++j) sw[(size_t)j * W + c] = sw[(size_t)(j + 1) * W + c];
+      sw[(size_t)(taps - 2) * W + c] = h0;
+    }
   }
 }
 
@@ -136,6 +145,7 @@ canon_norm_vec_kernel(CanonArgs a) {
 #pragma unroll
   for (int k = 0; k < TAPS; ++k) inv[k] = g / sqrtf(ss[k] / (float)W + a.eps);
   const float4* st4 = a.state != nullptr ? (const float4*)(a.state + (size_t)a.slots[seq] * (TAPS - 1) * W) : nullptr;
+  const bool single = TAPS > 1 && st4 != nullptr && a.cu_q[seq + 1] - a.cu_q[seq] == 1;
   T* h = (T*)a.h_out + (size_t)t * W;
   T* hc = (T*)a.hc_out + (size_t)t * W;
   for (int c = threadIdx.x; c < W4; c += blockDim.x) {
@@ -159,6 +169,7 @@ canon_norm_vec_kernel(CanonArgs a) {
     float acc[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[e] = h0[e] * w[e][TAPS - 1];
+    float4 before[TAPS];       // h of position t - k
 #pragma unroll
     for (int k = 1; k < TAPS; ++k) {
       float4 r;
@@ -168,11 +179,124 @@ canon_norm_vec_kernel(CanonArgs a) {
       } else {
         r = st4[(size_t)(TAPS - 1 + i - k) * W4 + c];
       }
+      before[k] = r;
       acc[0] = fmaf(r.x, w[0][TAPS - 1 - k], acc[0]); acc[1] = fmaf(r.y, w[1][TAPS - 1 - k], acc[1]);
       acc[2] = fmaf(r.z, w[2][TAPS - 1 - k], acc[2]); acc[3] = fmaf(r.w, w[3][TAPS - 1 - k], acc[3]);
     }
     store4<T>(h + 4 * c, h0[0], h0[1], h0[2], h0[3]);
     store4<T>(hc + 4 * c, h0[0] + acc[0], h0[1] + acc[1], h0[2] + acc[2], h0[3] + acc[3]);
+    if (single) {      // a sequence of one token: its state moves on here (this thread alone touches the channel)
+      float4* sw4 = (float4*)(a.state + (size_t)a.slots[seq] * (TAPS - 1) * W);
+#pragma unroll
+      for (int j = 0; j + 2 < TAPS; ++j) sw4[(size_t)j * W4 + c] = before[TAPS - 2 - j];
+      sw4[(size_t)(TAPS - 2) * W4 + c] = make_float4(h0[0], h0[1], h0[2], h0[3]);
+    }
+  }
+}
+
+// Many tokens: a block takes RUN consecutive tokens of the packed step.  First the factors of the run's rows and of
+// the TAPS - 1 rows before it (each row's sum of squares once per block), then every thread walks its channels down
+// the run with the last TAPS - 1 rows of h in registers.  A token whose sequence starts inside the run (or whose
+// earlier positions are not of this step) takes those rows from the state instead.
+template <typename T, int TAPS, int RUN>
+__global__ void __launch_bounds__(256)
+canon_norm_run_kernel(CanonArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int ROWS = RUN + TAPS - 1;
+  __shared__ float part[ROWS][8];
+  __shared__ float inv_s[ROWS];
+  __shared__ int first_s[RUN], slot_s[RUN], single_s[RUN];   // per token: its index among its sequence's tokens of
+                                                             // the step, its slot, whether it is the only one
+  const int t0 = blockIdx.x * RUN;
+  const int W = a.W, W4 = W >> 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float4* x4 = (const float4*)a.x;
+  if (threadIdx.x < RUN && t0 + threadIdx.x < a.n_tokens) {
+    const int seq = a.tok_seq[t0 + threadIdx.x];
+    first_s[threadIdx.x] = t0 + threadIdx.x - a.cu_q[seq];
+    slot_s[threadIdx.x] = a.slots[seq];
+    single_s[threadIdx.x] = TAPS > 1 && a.cu_q[seq + 1] - a.cu_q[seq] == 1;
+  }
+  float ss[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) ss[r] = 0.f;
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int t = t0 - (TAPS - 1) + r;
+      if (t >= 0 && t < a.n_tokens) {
+        const float4 v = x4[(size_t)t * W4 + c];
+        ss[r] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    ss[r] = warp_sum(ss[r]);
+    if (lane == 0) part[r][warp] = ss[r];
+  }
+  __syncthreads();
+  if (threadIdx.x < ROWS) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += part[threadIdx.x][w];
+    inv_s[threadIdx.x] = a.g[0] / sqrtf(s / (float)W + a.eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < W4; c += blockDim.x) {
+    float w[4][TAPS];          // the taps of channels 4 c to 4 c + 3: 4 TAPS numbers in a row
+    {
+      float flat[4 * TAPS];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) *(float4*)(flat + 4 * j) = *(const float4*)(a.taps_w + (size_t)4 * c * TAPS + 4 * j);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) w[e][j] = flat[e * TAPS + j];
+    }
+    float4 before[TAPS];       // before[k]: h of the packed token k places back
+#pragma unroll
+    for (int k = 1; k < TAPS; ++k) {
+      const int t = t0 - k;
+      float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t >= 0) {
+        const float f = inv_s[TAPS - 1 - k];
+        r = x4[(size_t)t * W4 + c];
+        r.x *= f; r.y *= f; r.z *= f; r.w *= f;
+      }
+      before[k] = r;
+    }
+#pragma unroll
+    for (int j = 0; j < RUN; ++j) {
+      const int t = t0 + j;
+      if (t < a.n_tokens) {
+        const int i = first_s[j];
+        const float f = inv_s[TAPS - 1 + j];
+        float4 v = x4[(size_t)t * W4 + c];
+        v.x *= f; v.y *= f; v.z *= f; v.w *= f;
+        float acc[4] = {v.x * w[0][TAPS - 1], v.y * w[1][TAPS - 1], v.z * w[2][TAPS - 1], v.w * w[3][TAPS - 1]};
+        float4 used[TAPS];
+#pragma unroll
+        for (int k = 1; k < TAPS; ++k) {
+          float4 r = before[k];
+          if (i - k < 0) r = ((const float4*)(a.state + (size_t)slot_s[j] * (TAPS - 1) * W))[(size_t)(TAPS - 1 + i - k) * W4 + c];
+          used[k] = r;
+          acc[0] = fmaf(r.x, w[0][TAPS - 1 - k], acc[0]); acc[1] = fmaf(r.y, w[1][TAPS - 1 - k], acc[1]);
+          acc[2] = fmaf(r.z, w[2][TAPS - 1 - k], acc[2]); acc[3] = fmaf(r.w, w[3][TAPS - 1 - k], acc[3]);
+        }
+        store4<T>((T*)a.h_out + (size_t)t * W + 4 * c, v.x, v.y, v.z, v.w);
+        store4<T>((T*)a.hc_out + (size_t)t * W + 4 * c, v.x + acc[0], v.y + acc[1], v.z + acc[2], v.w + acc[3]);
+        if (single_s[j]) {     // a sequence of one token: its state moves on here
+          float4* sw4 = (float4*)(a.state + (size_t)slot_s[j] * (TAPS - 1) * W);
+#pragma unroll
+          for (int r = 0; r + 2 < TAPS; ++r) sw4[(size_t)r * W4 + c] = used[TAPS - 2 - r];
+          sw4[(size_t)(TAPS > 1 ? TAPS - 2 : 0) * W4 + c] = v;
+        }
+#pragma unroll
+        for (int k = TAPS - 1; k >= 2; --k) before[k] = before[k - 1];
+        before[TAPS > 1 ? 1 : 0] = v;
+      }
+    }
   }
 }
 
@@ -187,6 +311,7 @@ canon_state_kernel(CanonArgs a) {
   const int seq = blockIdx.x;
   const int W = a.W, keep = a.taps - 1;
   const int begin = a.cu_q[seq], T = a.cu_q[seq + 1] - begin;
+  if (T == 1) return;          // canon_norm moved it on
   const float g = a.g[0];
   float* st = a.state + (size_t)a.slots[seq] * keep * W;
   for (int j = 0; j < keep; ++j) {
@@ -215,6 +340,7 @@ canon_state_vec_kernel(CanonArgs a) {
   const int seq = blockIdx.x;
   const int W = a.W, W4 = W >> 2;
   const int begin = a.cu_q[seq], T = a.cu_q[seq + 1] - begin;
+  if (T == 1) return;          // canon_norm moved it on
   const float g = a.g[0];
   const float4* x4 = (const float4*)a.x;
   float4* st4 = (float4*)(a.state + (size_t)a.slots[seq] * keep * W);
@@ -260,7 +386,16 @@ extern "C" int odi_canon_norm(const CanonArgs* args, int dtype, cudaStream_t str
 #define ODI_CANON_TAPS(T) switch (a.taps) { case 1: ODI_CANON(T, 1); break; case 2: ODI_CANON(T, 2); break; \
     case 3: ODI_CANON(T, 3); break; case 4: ODI_CANON(T, 4); break; case 5: ODI_CANON(T, 5); break; \
     case 6: ODI_CANON(T, 6); break; case 7: ODI_CANON(T, 7); break; default: ODI_CANON(T, 8); break; }
-  if (aligned && threads / 32 >= a.taps) {
+  if (aligned && threads / 32 >= a.taps && a.n_tokens < 512) {
+    if (dtype == 0) { ODI_CANON_TAPS(float) } else { ODI_CANON_TAPS(bf16) }
+    return launch_status();
+  }
+#undef ODI_CANON
+  if (aligned) {       // many tokens: runs of four, or of eight once those fill the device several times over
+    const int run = a.n_tokens < 4096 ? 4 : 8;
+#define ODI_CANON(T, K) if (run == 4) odi_rc = launch_pdl((canon_norm_run_kernel<T, K, 4>), dim3((a.n_tokens + 3) / 4), \
+        dim3(threads), 0, stream, a); \
+    else odi_rc = launch_pdl((canon_norm_run_kernel<T, K, 8>), dim3((a.n_tokens + 7) / 8), dim3(threads), 0, stream, a)
     if (dtype == 0) { ODI_CANON_TAPS(float) } else { ODI_CANON_TAPS(bf16) }
     return launch_status();
   }

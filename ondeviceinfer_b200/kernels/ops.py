@@ -1555,7 +1555,8 @@ def canon_norm(x, g, eps: float, taps_w, state, tok_seq, cu_q, slots, h_out, hc_
     """h = x / sqrt(mean(x^2) + eps) * g (``g`` one number) per token into ``h_out``, and h + conv(h) into ``hc_out``
     (both in the compute dtype), conv(h)_t = sum_j taps_w[:, j] h_(t - taps + 1 + j) over the sequence's earlier
     tokens: those of this step, and before them ``state[slot]`` [taps - 1, width] (fp32: h of the sequence's last
-    positions, zero before its start).  The state is not changed: :func:`canon_state` moves it on afterwards."""
+    positions, zero before its start).  The state of a sequence that brings one token is moved on in the same
+    launch; :func:`canon_state` moves on the others afterwards."""
     args = _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, h_out, hc_out, eps)
     _require(h_out, "h_out", ndim=2)
     _require(hc_out, "hc_out", h_out.dtype, 2)
@@ -1567,7 +1568,8 @@ def canon_norm(x, g, eps: float, taps_w, state, tok_seq, cu_q, slots, h_out, hc_
 
 def canon_state(x, g, eps: float, taps_w, state, tok_seq, cu_q, slots) -> None:
     """After :func:`canon_norm` and before ``x`` changes: ``state[slot]`` becomes h of the last taps - 1 positions
-    of every sequence of the step (rows of the old state move up where a sequence brought fewer tokens)."""
+    of every sequence that brought more than one token (rows of the old state move up where it brought fewer than
+    taps - 1); a step of single tokens needs no call."""
     if taps_w.shape[1] <= 1:
         return
     args = _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, None, None, eps)

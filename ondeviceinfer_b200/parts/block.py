@@ -159,7 +159,8 @@ class ParallelBlock(Part):
     ``ops.canon_norm`` makes h and h + conv(h) in one pass over the stream (the norm's weight is one number);
     the rows of h before a sequence's first token of the step come from the sequence's state, the fp32 h of its
     last taps - 1 positions (a :class:`~ondeviceinfer_b200.cache.StateNeed` of the block, zero when a sequence
-    starts), which ``ops.canon_state`` moves on.  The mixer's fp32 output (a part that says ``returns_output``
+    starts), which the same launch moves on for a sequence that brings one token and ``ops.canon_state`` for the
+    others.  The mixer's fp32 output (a part that says ``returns_output``
     returns it; any other adds into a zeroed buffer) takes the feed-forward's as its residual add, and
     ``ops.scaled_add`` adds the sum to the stream."""
 
@@ -213,7 +214,8 @@ class ParallelBlock(Part):
         eps = self.norm.spec.eps
         from ..kernels import ops
         ops.canon_norm(hidden, self.norm.scalar, eps, self.taps_w, state, ctx.tok_seq, ctx.cu_q, ctx.slots, h, hc)
-        ops.canon_state(hidden, self.norm.scalar, eps, self.taps_w, state, ctx.tok_seq, ctx.cu_q, ctx.slots)
+        if ctx.max_q_len > 1:       # the state of a sequence that brings one token moved on in the launch above
+            ops.canon_state(hidden, self.norm.scalar, eps, self.taps_w, state, ctx.tok_seq, ctx.cu_q, ctx.slots)
         if getattr(self.mixer, "returns_output", False):
             branch = self.mixer.forward(hc, ctx, view, None)
         else:

@@ -77,15 +77,23 @@ def ints(*values):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,width", [(1, 24), (2, 40), (3, 64), (5, 100), (8, 1032)])
-def test_norm_and_convolution_with_state_over_cut_sequences(dtype, taps, width):
+@pytest.mark.parametrize("taps,width,steps", [(1, 24, "short"), (2, 40, "short"), (3, 64, "short"), (5, 100, "short"),
+                                              (8, 1032, "short"), (1, 24, "long"), (3, 40, "long"), (4, 136, "long"),
+                                              (8, 72, "long")])
+def test_norm_and_convolution_with_state_over_cut_sequences(dtype, taps, width, steps):
     """Three sequences cut into unequal runs (runs shorter than the taps among them): h and h + conv(h) of every run
-    against the plain norm and convolution of the whole sequences."""
+    against the plain norm and convolution of the whole sequences.  The long steps carry hundreds and thousands of
+    tokens (the kernel whose blocks take runs of four or eight tokens), single tokens of other sequences among them,
+    and sequences that start in the middle of a block's run."""
     g = torch.Generator().manual_seed(taps)
     eps, scalar = 1e-5, torch.tensor([1.3])
     w = (0.5 * torch.randn(width, taps, generator=g))
-    lengths = [23, 9, 40]
-    cuts = [[1, 1, 2, 7, 1, 11], [4, 1, 1, 3], [17, 1, 1, 1, 20]]
+    if steps == "short":
+        lengths = [23, 9, 40]
+        cuts = [[1, 1, 2, 7, 1, 11], [4, 1, 1, 3], [17, 1, 1, 1, 20]]
+    else:
+        lengths = [5000, 9, 903]
+        cuts = [[4299, 1, 699, 1], [3, 1, 1, 4], [1, 298, 1, 603]]
     xs = [torch.randn(n, width, generator=g) * (1 + torch.arange(n)[:, None] % 3) for n in lengths]
     state = torch.full((5, max(taps - 1, 1), width), 9.0, device="cuda")[:, :taps - 1].contiguous() if taps > 1 else None
     slots = [3, 0, 2]
@@ -94,7 +102,7 @@ def test_norm_and_convolution_with_state_over_cut_sequences(dtype, taps, width):
     got_h = [[] for _ in lengths]
     got_hc = [[] for _ in lengths]
     at = [0, 0, 0]
-    for step in range(6):
+    for step in range(max(len(c) for c in cuts)):
         live = [s for s in range(3) if step < len(cuts[s])]
         runs = [xs[s][at[s]:at[s] + cuts[s][step]] for s in live]
         x = torch.cat(runs).cuda()
