@@ -140,10 +140,50 @@ latent_expand_kernel(LatentExpandArgs a) {
   }
 }
 
+// The same in 16-byte pieces, a block per token: every size a multiple of a piece's lanes, every pointer aligned.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_expand_vec_kernel(LatentExpandArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int CH = 16 / (int)sizeof(T);      // lanes of a piece
+  const int t = blockIdx.x;
+  const int seq = a.tok_seq[t];
+  const int li = t - a.cu_q[seq];
+  const size_t page = (size_t)(a.page_start[seq] + li / a.page_size) * a.heads;
+  const int in_page = li % a.page_size;
+  const int pieces = a.Dh / CH;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  const T* kr = (const T*)a.key_rot + (size_t)t * a.r;
+  for (int i = threadIdx.x; i < a.heads * pieces; i += blockDim.x) {
+    const int h = i / pieces, lane = (i % pieces) * CH;
+    const size_t slot = (page + h) * a.page_size + in_page;
+    const T* qp = (const T*)a.proj + (size_t)t * a.ld + h * (a.d + a.r);
+    const T* qr = (const T*)a.q_abs + ((size_t)t * a.heads + h) * a.row + a.R;
+    const T* kp = (const T*)a.k_plain + ((size_t)t * a.heads + h) * a.d;
+    const T* vp = (const T*)a.v + ((size_t)t * a.heads + h) * a.dv;
+    const bool plain = lane < a.d, rotated = !plain && lane < a.d + a.r;
+    const uint4 q = plain ? *(const uint4*)(qp + lane) : (rotated ? *(const uint4*)(qr + lane - a.d) : zero);
+    const uint4 k = plain ? *(const uint4*)(kp + lane) : (rotated ? *(const uint4*)(kr + lane - a.d) : zero);
+    const uint4 v = lane < a.dv ? *(const uint4*)(vp + lane) : zero;
+    *(uint4*)((T*)a.q_full + ((size_t)t * a.heads + h) * a.Dh + lane) = q;
+    *(uint4*)((T*)a.k_pool + slot * a.Dh + lane) = k;
+    *(uint4*)((T*)a.v_pool + slot * a.Dh + lane) = v;
+  }
+}
+
 extern "C" int odi_latent_expand(const LatentExpandArgs* args, int dtype, cudaStream_t stream) {
   const LatentExpandArgs a = *args;
   if (a.n_tokens <= 0) return 0;
   if (a.Dh < a.d + a.r || a.Dh < a.dv || a.heads <= 0 || a.heads > 65535) return ODI_ERR_ARGUMENT;
+  const int ch = dtype == 0 ? 4 : 8;
+  const uintptr_t pointers = (uintptr_t)a.proj | (uintptr_t)a.q_abs | (uintptr_t)a.k_plain | (uintptr_t)a.key_rot |
+                             (uintptr_t)a.v | (uintptr_t)a.q_full | (uintptr_t)a.k_pool | (uintptr_t)a.v_pool;
+  if ((a.d | a.r | a.dv | a.Dh | a.ld | a.row | a.R) % ch == 0 && (pointers & 15) == 0) {
+    if (dtype == 0) odi_rc = launch_pdl((latent_expand_vec_kernel<float>), dim3(a.n_tokens), dim3(256), 0, stream, a);
+    else odi_rc = launch_pdl((latent_expand_vec_kernel<bf16>), dim3(a.n_tokens), dim3(256), 0, stream, a);
+    return launch_status();
+  }
   const dim3 grid(a.n_tokens, a.heads);
   if (dtype == 0) odi_rc = launch_pdl((latent_expand_kernel<float>), grid, dim3(128), 0, stream, a);
   else odi_rc = launch_pdl((latent_expand_kernel<bf16>), grid, dim3(128), 0, stream, a);

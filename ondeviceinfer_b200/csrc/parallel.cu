@@ -16,7 +16,8 @@
 // Norms, the convolution's sum and the powers are fp32 in both compute dtypes; each output is rounded once.
 #include "common.cuh"
 
-#define CANON_MAX_TAPS 8
+#define CANON_MAX_TAPS 8          // the forms with 16-byte accesses keep the taps' factors in registers
+#define CANON_MOST_TAPS 64        // the plain form keeps them in shared memory
 
 struct CanonArgs {
   const float* x;        // [n_tokens, W] the stream
@@ -38,23 +39,20 @@ canon_norm_kernel(CanonArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
+  __shared__ float inv[CANON_MOST_TAPS];
   const int t = blockIdx.x;
   const int seq = a.tok_seq[t];
   const int i = t - a.cu_q[seq];            // index among the tokens that the sequence brings in this step
   const int W = a.W, taps = a.taps;
   const float g = a.g[0];
-  float inv[CANON_MAX_TAPS];
-#pragma unroll
-  for (int k = 0; k < CANON_MAX_TAPS; ++k) {
-    inv[k] = 0.f;
-    if (k < taps && i - k >= 0) {
-      const float* xr = a.x + (size_t)(t - k) * W;
-      float ss = 0.f;
-      for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
-      ss = block_sum(ss, scratch);
-      inv[k] = g / sqrtf(ss / (float)W + a.eps);
-    }
+  for (int k = 0; k < taps && i - k >= 0; ++k) {
+    const float* xr = a.x + (size_t)(t - k) * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) inv[k] = g / sqrtf(ss / (float)W + a.eps);
   }
+  __syncthreads();
   const float* st = a.state != nullptr ? a.state + (size_t)a.slots[seq] * (taps - 1) * W : nullptr;
   const bool single = st != nullptr && a.cu_q[seq + 1] - a.cu_q[seq] == 1;
   T* h = (T*)a.h_out + (size_t)t * W;
@@ -63,13 +61,10 @@ canon_norm_kernel(CanonArgs a) {
     const float h0 = a.x[(size_t)t * W + c] * inv[0];
     const float* w = a.taps_w + (size_t)c * taps;
     float acc = h0 * w[taps - 1];
-#pragma unroll
-    for (int k = 1; k < CANON_MAX_TAPS; ++k) {
-      if (k < taps) {
-        // position t - k: a token of this step, or row (taps - 1) + (i - k) of the state
-        const float hk = i - k >= 0 ? a.x[(size_t)(t - k) * W + c] * inv[k] : st[(size_t)(taps - 1 + i - k) * W + c];
-        acc = fmaf(hk, w[taps - 1 - k], acc);
-      }
+    for (int k = 1; k < taps; ++k) {
+      // position t - k: a token of this step, or row (taps - 1) + (i - k) of the state
+      const float hk = i - k >= 0 ? a.x[(size_t)(t - k) * W + c] * inv[k] : st[(size_t)(taps - 1 + i - k) * W + c];
+      acc = fmaf(hk, w[taps - 1 - k], acc);
     }
     h[c] = from_f<T>(h0);
     hc[c] = from_f<T>(h0 + acc);
@@ -378,10 +373,10 @@ canon_state_vec_kernel(CanonArgs a) {
 extern "C" int odi_canon_norm(const CanonArgs* args, int dtype, cudaStream_t stream) {
   const CanonArgs a = *args;
   if (a.n_tokens <= 0) return 0;
-  if (a.taps < 1 || a.taps > CANON_MAX_TAPS || a.W <= 0 || (a.taps > 1 && a.state == nullptr)) return ODI_ERR_UNSUPPORTED;
+  if (a.taps < 1 || a.taps > CANON_MOST_TAPS || a.W <= 0 || (a.taps > 1 && a.state == nullptr)) return ODI_ERR_UNSUPPORTED;
   const int threads = a.W >= 1024 ? 256 : 128;
-  const bool aligned = a.W % 4 == 0 && (((uintptr_t)a.x | (uintptr_t)a.state | (uintptr_t)a.h_out | (uintptr_t)a.hc_out |
-                                         (uintptr_t)a.taps_w) & 15) == 0;
+  const bool aligned = a.taps <= CANON_MAX_TAPS && a.W % 4 == 0 &&
+                       (((uintptr_t)a.x | (uintptr_t)a.state | (uintptr_t)a.h_out | (uintptr_t)a.hc_out | (uintptr_t)a.taps_w) & 15) == 0;
 #define ODI_CANON(T, K) odi_rc = launch_pdl((canon_norm_vec_kernel<T, K>), dim3(a.n_tokens), dim3(threads), 0, stream, a)
 #define ODI_CANON_TAPS(T) switch (a.taps) { case 1: ODI_CANON(T, 1); break; case 2: ODI_CANON(T, 2); break; \
     case 3: ODI_CANON(T, 3); break; case 4: ODI_CANON(T, 4); break; case 5: ODI_CANON(T, 5); break; \
@@ -409,9 +404,9 @@ extern "C" int odi_canon_norm(const CanonArgs* args, int dtype, cudaStream_t str
 extern "C" int odi_canon_state(const CanonArgs* args, cudaStream_t stream) {
   const CanonArgs a = *args;
   if (a.n_seqs <= 0 || a.taps <= 1) return 0;
-  if (a.taps > CANON_MAX_TAPS || a.state == nullptr) return ODI_ERR_UNSUPPORTED;
+  if (a.taps > CANON_MOST_TAPS || a.state == nullptr) return ODI_ERR_UNSUPPORTED;
   const int threads = a.W >= 1024 ? 256 : 128;
-  if (a.W % 4 == 0 && (((uintptr_t)a.x | (uintptr_t)a.state) & 15) == 0 && threads / 32 >= a.taps) {
+  if (a.taps <= CANON_MAX_TAPS && a.W % 4 == 0 && (((uintptr_t)a.x | (uintptr_t)a.state) & 15) == 0 && threads / 32 >= a.taps) {
 #define ODI_STATE(K) odi_rc = launch_pdl((canon_state_vec_kernel<K>), dim3(a.n_seqs), dim3(threads), 0, stream, a)
     switch (a.taps) {
       case 2: ODI_STATE(2); break; case 3: ODI_STATE(3); break; case 4: ODI_STATE(4); break; case 5: ODI_STATE(5); break;

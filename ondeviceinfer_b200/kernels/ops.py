@@ -1530,7 +1530,7 @@ class _CanonArgs(Structure):
                 ("n_seqs", c_int), ("W", c_int), ("taps", c_int), ("eps", c_float)]
 
 
-CANON_MAX_TAPS = 8
+CANON_MAX_TAPS = 64       # the plain kernel keeps the taps' factors in shared memory; up to 8 taps take the 16-byte forms
 
 
 def _canon_args(x, g, taps_w, state, tok_seq, cu_q, slots, h_out, hc_out, eps) -> _CanonArgs:

@@ -173,6 +173,8 @@ class ParallelBlock(Part):
             raise TypeError("this block's norm has one number as its weight and scales in fp32")
         if spec.conv_taps < 1 or (spec.conv_name is None and spec.conv_taps != 1):
             raise ValueError("conv_taps is at least 1, and 1 without a convolution")
+        if spec.conv_taps > 64:
+            raise ValueError(f"the convolution kernels take up to 64 taps, got {spec.conv_taps}")
         self.taps = spec.conv_taps if spec.conv_name is not None else 1
 
     def _children(self):
