@@ -164,6 +164,7 @@ ALL_SOURCES = {
                       + [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512, "ODI_SHARED_KV": 1}],      # a latent cache
     "latent": [{}],
     "capped": [{}],
+    "parallel": [{}],
     "attention_capped_mma": [{"ODI_HEAD_DIM": 128, "ODI_VALUE_DIM": 128}],
     "attention_latent_mma": [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512}],      # a latent cache, on the tensor cores
     "grouped_gemm": [{}],

@@ -1092,7 +1092,10 @@ def grouped_gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, a_c
                         None, None, None, None, None, a_stride, N * K, c_stride, a.shape[1], K, c.shape[1], M, N, K,
                         groups, 1, GROUPED_STORE_F32 if out_f32 else GROUPED_STORE, 0.0, 0.0)
     lib = load_library("grouped_gemm")
-    tm = grouped_rows_tile(M, M <= 2 * FEW_ROWS and bool(lib.odi_grouped_gemm_takes_few_rows(byref(args))))
+    # up to four rows: the form that streams the weights; five to eight rows too when the inner size is long (the
+    # tile form would walk it in a few blocks per head), in two row tiles; else tiles of 16 or 64 rows
+    few = M <= 2 * FEW_ROWS and (M <= FEW_ROWS or K >= 256) and bool(lib.odi_grouped_gemm_takes_few_rows(byref(args)))
+    tm = FEW_ROWS if few else grouped_rows_tile(M)
     _check(lib.odi_grouped_gemm(byref(args), c_int(0), c_int(tm), c_int(dtype_code(w.dtype)), _stream()), "grouped_gemm")
 
 

@@ -151,6 +151,7 @@ def test_routed_products_against_a_loop_over_pairs(dtype, tokens, K, F):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,K,N,M,a_gap,c_gap", [(3, 10, 7, 37, 2, 4), (4, 16, 12, 3, 8, 4), (4, 16, 12, 7, 8, 4),
                                                      (2, 24, 70, 130, 8, 2),
+                                                     (3, 264, 20, 7, 8, 4), (4, 512, 40, 8, 0, 8), (2, 256, 9, 5, 8, 3),   # five to eight rows, long inner size: two row tiles of the form for few rows
                                                      (2400, 16, 320, 3, 8, 4)])     # bf16: more than 32 items a warp
 def test_products_per_head(dtype, heads, K, N, M, a_gap, c_gap):
     g = torch.Generator().manual_seed(3)
