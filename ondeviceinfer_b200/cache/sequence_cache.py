@@ -14,7 +14,9 @@ fixed-size per-sequence state.
 * Layers whose mixers ask for the same thing form a **group** with storage of its own:
   all layers that keep every key (``KVNeed`` without window), all layers that keep a
   window of the same size, all layers with the same ``StateNeed``.  A windowed group
-  keeps a ring of pages per sequence instead of all of them.
+  keeps a ring of pages per sequence instead of all of them; if it also keeps a sequence's
+  first positions for good (``KVNeed.keep_first``), the pages of those positions are pinned in
+  front of the ring and never used again while the sequence lives.
 * The layout of a key/value pool is ``[owner, 2, page, kv_head, row, head_dim]``
   (owner = a layer execution that writes its own cache; 2 = keys, values), so one
   (page, head) tile is a dense ``[PAGE_SIZE, head_dim]`` box.  Values whose width differs
@@ -34,6 +36,7 @@ from .allocators import CacheCapacityError, IndexAllocator
 from .needs import KVNeed, StateNeed
 
 PAGE_SIZE = 64
+RING_PINNED_UNIT = 65536      # KVGroup.ring_pages = pinned pages * this + pages of the ring
 
 
 def pages_for(tokens: int) -> int:
@@ -46,11 +49,19 @@ class KVGroup:
     def __init__(self, index: int, need: KVNeed, owners: List[int], n_pages: int, n_slots: int,
                  dtype: torch.dtype, device, max_step_tokens: int) -> None:
         self.index, self.need, self.owners = index, need, owners
-        if need.window is None:
-            self.ring_pages = 0
-        else:
+        # `ring_pages` is what the kernels take (csrc/common.cuh: page_slot_of): 0 for a group that keeps every
+        # page, else pinned * 65536 + ring: the first `pinned` pages of a sequence stay, the later ones go round
+        # a ring of `ring` pages
+        self.pinned_pages = self.ring_len = 0
+        if need.keep_first < 0 or (need.keep_first > 0 and need.window is None):
+            raise ValueError("keep_first is a number of positions kept beside a window")
+        if need.window is not None:
             # positions [p - window + 1, p + step - 1] must map to distinct rows of the ring
-            self.ring_pages = pages_for(need.window + max_step_tokens - 1) + 1
+            self.ring_len = pages_for(need.window + max_step_tokens - 1) + 1
+            self.pinned_pages = pages_for(need.keep_first)
+            if self.ring_len >= RING_PINNED_UNIT or self.pinned_pages >= 32768:
+                raise ValueError(f"a ring of {self.ring_len} pages behind {self.pinned_pages} pinned ones is beyond the kernels' page index")
+        self.ring_pages = self.pinned_pages * RING_PINNED_UNIT + self.ring_len
         # one page and one slot beyond the capacity belong to padding rows of fixed-width steps
         self.planes = 2 if need.value_plane else 1
         # values of a width of their own live in a second pool of the same page numbering
@@ -66,7 +77,7 @@ class KVGroup:
 
     def pages_needed(self, length: int) -> int:
         n = pages_for(length)
-        return n if self.ring_pages == 0 else min(n, self.ring_pages)
+        return n if self.ring_len == 0 else min(n, self.pinned_pages + self.ring_len)
 
     def keys(self, owner_pos: int) -> torch.Tensor:
         return self.pool[owner_pos, 0]

@@ -108,8 +108,12 @@ class CappedAttentionSpec:
     ``sink``: the softmax has one more term, of score 0 and without a value: p_j = exp(s_j) / (1 + sum_k exp(s_k)).
     ``values_are_keys``: there is no value projection; a head's value is its key as projected, before the rotation
     (``value_dim`` == ``head_dim``).
+    ``keep_first`` k > 0 (with a window): keys 0..k-1 of a sequence stay visible beyond the window, at their true
+    positions: position p sees j <= p with p - j < w or j < k.
     ``names`` maps the roles q, k, v, o to tensor names below ``prefix``; when it also names q_bias or k_bias, that
-    projection adds the [out] bias of that name."""
+    projection adds the [out] bias of that name; when it names q_norm and k_norm (with ``unit_norm_eps``), every
+    query resp. key head is multiplied, after the division, by that [head_dim] weight, which the heads share (an RMS
+    norm per head with a plain weight)."""
 
     hidden_size: int
     num_heads: int
@@ -125,6 +129,7 @@ class CappedAttentionSpec:
     unit_norm_eps: Optional[float] = None
     sink: bool = False
     values_are_keys: bool = False
+    keep_first: int = 0
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
@@ -145,7 +150,8 @@ class LatentAttentionSpec:
     (p itself included).  ``position`` rotates the ``rot_dim`` lanes.
     ``q_rank`` not None: the queries go through a latent of their own, q = W_uq RMSnorm(W_dq h) (plain weight,
     ``norm_eps``; roles dq, dq_norm, uq instead of q).  ``gated``: the concatenated heads are multiplied by
-    sigmoid(W_g h) before the output projection (role g).  ``own_kv`` False: the layer has no down projection and
+    sigmoid(W_g h) before the output projection (role g: one row of W_g per lane of the heads, or with
+    ``gate_per_head`` one row per head, whose number multiplies all of the head's lanes).  ``own_kv`` False: the layer has no down projection and
     reads the cache rows that another layer execution wrote (the plan's order says which), with its own
     up-projections, queries and window; ``keep`` is then the window that the shared rows are kept for (None: all
     of them), at least the window of every layer that reads them.
@@ -168,6 +174,7 @@ class LatentAttentionSpec:
     keeps_all: bool = False         # the cache keeps every position although this layer has a window (a reader has none)
     gated: bool = False
     own_kv: bool = True
+    gate_per_head: bool = False
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
@@ -220,7 +227,11 @@ class RoutedExpertsSpec:
     ``num_identity`` outputs pass the input on; the others are experts
     down(g * sigmoid(``gate_alpha`` g) * (u + 1)), g = min(gate x, ``limit``), u = clamp(up x, +-``limit``).
     ``shared_size`` > 0 adds one expert of that form (its own ``shared_limit``) for every token.
-    Tensor names below ``prefix``: ``router``, ``correction``, ``e<i>.gate|up|down``, ``shared.gate|up|down``."""
+    ``scoring`` "sigmoid": the score of an output is the logistic function of its logit instead of the softmax.
+    ``expert_form`` "relu2": an expert (and the shared one) is down(max(up x, 0)^2), without gate, limit or bias.
+    ``weight_on_input``: a chosen expert's weight multiplies its input, out = sum_k expert_k(w_k x), not its output.
+    Tensor names below ``prefix``: ``router``, ``correction``, ``e<i>.gate|up|down``, ``shared.gate|up|down``
+    (no ``gate`` tensors for ungated experts)."""
 
     hidden_size: int
     expert_size: int
@@ -235,6 +246,9 @@ class RoutedExpertsSpec:
     shared_size: int = 0
     shared_limit: float = 0.0
     gate_alpha: float = 1.702
+    scoring: str = "softmax"
+    expert_form: str = "gated_clamp"
+    weight_on_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -285,6 +299,85 @@ class PolyNormMLPSpec:
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
+class ClampedGatedMLPSpec:
+    """Dense gated feed-forward with clamped halves: g = min(gate x, ``limit``), u = clamp(up x, -limit, limit),
+    y = g * sigmoid(``alpha`` g) * (u + 1), output down y.  ``names`` maps the roles gate, up, down to tensor names
+    below ``prefix``; when it also names gate_bias, up_bias or down_bias, that projection adds the bias."""
+
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+    alpha: float = 1.702
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+    def has(self, role: str) -> bool:
+        return role in dict(self.names)
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A selective state-space mixer with one scalar decay per head (the recurrent form of the state-space duality).
+
+    inner = ``num_heads`` * ``head_dim``.  One projection of the input gives [z: inner | x: inner | B: G N | C: G N |
+    dt: heads] (G = ``groups``, N = ``state_dim``).  x, B and C together pass a causal convolution per channel
+    (``conv_taps`` taps, the last one the current token's, zeros before the start, a bias) and SiLU.
+    dt = softplus(dt + dt_bias).  Per head h (group h // (heads / G)), with S [N, head_dim] zero at the start:
+    S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T;  y_t = S_t^T C_t + D_h x_t.  y (heads side by side) is
+    multiplied by silu(z), RMS-normed in ``norm_groups`` equal parts (``norm_eps`` inside each root), multiplied by a
+    weight per lane, and projected by o.  The state and the convolution's last taps - 1 inputs are fp32 and are
+    carried from token to token per sequence.  ``names`` maps the roles in, conv, conv_bias, dt_bias, A_log, D, norm,
+    o to tensor names below ``prefix``."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    prefix: str
+    names: Tuple[Tuple[str, str], ...]
+
+    def name(self, role: str) -> str:
+        return self.prefix + dict(self.names)[role]
+
+
+@dataclass(frozen=True)
+class SideBySideMixersSpec:
+    """Two mixers that read the same input; the result is ``left_scale`` * left + ``right_scale`` * right.  Each
+    keeps the cache or state that it would keep alone (at most one of them keys and values)."""
+
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class TokenSideInputSpec:
+    """A per-layer input looked up by token id, added to the stream after a layer: e = lanes [``col``, ``col`` +
+    ``dim``) of row ``token id`` of ``table_name`` [``vocab_size``, ``table_width``]; g = gelu_tanh(gate x) * e with
+    gate [dim, hidden]; y = proj g with proj [hidden, dim]; x <- x + y / sqrt(mean(y^2) + ``eps``) * norm (a plain
+    weight).  The norm and the add are fp32."""
+
+    hidden_size: int
+    vocab_size: int
+    dim: int
+    table_width: int
+    col: int
+    table_name: str
+    gate_name: str
+    proj_name: str
+    norm_name: str
+    eps: float
 
 
 @dataclass(frozen=True)
@@ -342,6 +435,24 @@ class ParallelBlockSpec:
 
 
 @dataclass(frozen=True)
+class ScaledParallelBlockSpec:
+    """x <- x + s1 * mixer(norm1(x)) + s2 * feed_forward(norm2(x)): both sublayers read the same x through a norm of
+    their own, and each output is multiplied lane by lane by a stored vector (``mixer_scale_name``,
+    ``ffn_scale_name``: [hidden]) before the sum.  ``ffn`` None (with its norm and scale): the layer has no
+    feed-forward.  ``after`` (a spec of a part with ``forward(hidden, ctx, copy)``, or None) then adds to the new
+    stream.  Norms, scales and sums are fp32."""
+
+    mixer_norm: object
+    mixer: object
+    ffn_norm: object
+    ffn: object
+    hidden_size: int
+    mixer_scale_name: str
+    ffn_scale_name: Optional[str] = None
+    after: object = None
+
+
+@dataclass(frozen=True)
 class ReinjectSpec:
     """A step between layers that keeps no cache: h <- W [h ; e] + steps[index], with e the output of the
     embedding, W [hidden, 2 hidden] (the columns of h first) and ``steps`` [``num_steps``, hidden].  It opens a
@@ -370,13 +481,16 @@ class OrderEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """Token embedding: hidden[t] = table[token[t]], no scaling, nothing added; with ``norm`` (a norm spec) the
-    rows then pass that norm, in fp32."""
+    """Token embedding: hidden[t] = table[token[t]] * ``scale``; with ``sinusoid_base`` b an absolute position
+    vector is added, entry 2i = sin(p b^(-2i / hidden_size)), entry 2i + 1 = the cosine of the same angle, p the
+    token's position in its sequence (fp32); with ``norm`` (a norm spec) the rows then pass that norm, in fp32."""
 
     vocab_size: int
     hidden_size: int
     weight_name: str
     norm: object = None
+    scale: float = 1.0
+    sinusoid_base: Optional[float] = None
 
 
 @dataclass(frozen=True)

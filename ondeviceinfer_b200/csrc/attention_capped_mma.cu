@@ -9,7 +9,9 @@
 //
 //   score = q . k * scale;  with softcap c > 0: score <- c tanh(score / c);  with sink = 1 the softmax has one more
 //   term, of score 0 and without a value: p_j = e^(s_j) / (1 + sum_k e^(s_k));
-//   key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window).
+//   key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window or j < keep): with
+//   keep > 0 a windowed layer goes on seeing the first `keep` positions of its sequence; their tiles come first in
+//   a block's walk, then the tiles of the window.
 //
 // Key and value tiles (64 positions x D resp. DV bf16, contiguous in a page) are copied with cp.async, double
 // buffered, one block barrier per tile, into rows padded by 16 bytes so that ldmatrix reads are free of bank
@@ -51,6 +53,7 @@ struct CappedAttnArgs {
   int n_seqs, nq, nkv, ring_pages, window;
   float scale, softcap;
   int sink;               // 1: the softmax has one more term, of score 0 and without a value
+  int keep;               // > 0 with a window: keys 0..keep-1 stay visible beyond the window
 };
 
 // 1 / (l + 2^-m) for row sums l taken relative to the maximum m (log2 domain): the denominator with the sink's
@@ -123,6 +126,10 @@ attention_capped_kernel(CappedAttnArgs a) {
   const int nt = min(64, q_len - t0);
   const int first_key = a.window > 0 ? max(0, past + t0 - a.window + 1) : 0;     // the oldest key any row sees
   const int tile_lo = first_key / KT, tile_hi = (past + t0 + nt - 1) / KT;       // inclusive
+  // the walk: the tiles of kept first keys in front of the window's first tile, then tile_lo..tile_hi
+  const int keep_tiles = a.window > 0 && a.keep > 0 ? min((a.keep + KT - 1) / KT, tile_lo) : 0;
+  const int n_walk = keep_tiles + tile_hi - tile_lo + 1;
+  auto tile_of = [&](int w) { return w < keep_tiles ? w : tile_lo + (w - keep_tiles); };
   const int* pages = a.page_ids + a.page_start[seq];
 
   // this warp's rows: tokens t0 + warp*16 + {lane/4, lane/4 + 8}
@@ -150,24 +157,24 @@ attention_capped_kernel(CappedAttnArgs a) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   const float two_over_cap = a.softcap > 0.f ? 2.f / a.softcap : 0.f;
 
-  auto issue = [&](int tile) {
-    uint8_t* st = smem + (size_t)((tile - tile_lo) % STAGES) * (K_BYTES + V_BYTES);
-    const int page = pages[a.ring_pages > 0 ? tile % a.ring_pages : tile];
+  auto issue = [&](int w) {
+    uint8_t* st = smem + (size_t)(w % STAGES) * (K_BYTES + V_BYTES);
+    const int page = pages[page_slot_of_page(tile_of(w), a.ring_pages)];
     const size_t row0 = ((size_t)page * a.nkv + hk) * KT;
     load_tile<D, ROWB_K>(st, a.k_pool + row0 * D, tid);
     load_tile<DV, ROWB_V>(st + K_BYTES, a.v_pool + row0 * DV, tid);
     cp_async_commit();
   };
-  issue(tile_lo);
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    if (tile < tile_hi) { issue(tile + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+  issue(0);
+  for (int w = 0; w < n_walk; ++w) {
+    if (w + 1 < n_walk) { issue(w + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     __syncthreads();
-    const uint8_t* st = smem + (size_t)((tile - tile_lo) % STAGES) * (K_BYTES + V_BYTES);
+    const uint8_t* st = smem + (size_t)(w % STAGES) * (K_BYTES + V_BYTES);
     const uint32_t k_smem = smem_addr(st), v_smem = k_smem + K_BYTES;
-    const int kbase = tile * KT;
+    const int kbase = tile_of(w) * KT;
     // a warp whose rows all lie before this tile, or all see only later keys, has nothing to add
     const int warp_first = past + t0 + warp * 16, warp_last = warp_first + 15;
-    const bool active = kbase <= warp_last && (a.window == 0 || kbase + KT - 1 > warp_first - a.window);
+    const bool active = kbase <= warp_last && (a.window == 0 || kbase + KT - 1 > warp_first - a.window || kbase < a.keep);
     if (active) {
       float s[8][4];
 #pragma unroll
@@ -190,10 +197,10 @@ attention_capped_kernel(CappedAttnArgs a) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int kj = kbase + i * 8 + (lane & 3) * 2;
-        s[i][0] = (kj <= pos_lo && kj >= old_lo) ? shape_score(s[i][0], a.scale, a.softcap, two_over_cap) : -INFINITY;
-        s[i][1] = (kj + 1 <= pos_lo && kj + 1 >= old_lo) ? shape_score(s[i][1], a.scale, a.softcap, two_over_cap) : -INFINITY;
-        s[i][2] = (kj <= pos_hi && kj >= old_hi) ? shape_score(s[i][2], a.scale, a.softcap, two_over_cap) : -INFINITY;
-        s[i][3] = (kj + 1 <= pos_hi && kj + 1 >= old_hi) ? shape_score(s[i][3], a.scale, a.softcap, two_over_cap) : -INFINITY;
+        s[i][0] = (kj <= pos_lo && (kj >= old_lo || kj < a.keep)) ? shape_score(s[i][0], a.scale, a.softcap, two_over_cap) : -INFINITY;
+        s[i][1] = (kj + 1 <= pos_lo && (kj + 1 >= old_lo || kj + 1 < a.keep)) ? shape_score(s[i][1], a.scale, a.softcap, two_over_cap) : -INFINITY;
+        s[i][2] = (kj <= pos_hi && (kj >= old_hi || kj < a.keep)) ? shape_score(s[i][2], a.scale, a.softcap, two_over_cap) : -INFINITY;
+        s[i][3] = (kj + 1 <= pos_hi && (kj + 1 >= old_hi || kj + 1 < a.keep)) ? shape_score(s[i][3], a.scale, a.softcap, two_over_cap) : -INFINITY;
         mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
         mx_hi = fmaxf(mx_hi, fmaxf(s[i][2], s[i][3]));
       }
@@ -282,9 +289,13 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
   const int tok = a.cu_q[seq];
   const int pos = a.past[seq];                     // the query's position
   const int first_key = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int tile_lo = first_key / KT, n_tiles = pos / KT + 1 - tile_lo;
+  // the walk over all splits: the tiles of kept first keys in front of the window's first tile, then the window's
+  const int tile_lo = first_key / KT;
+  const int keep_tiles = a.window > 0 && a.keep > 0 ? min((a.keep + KT - 1) / KT, tile_lo) : 0;
+  const int n_tiles = keep_tiles + pos / KT + 1 - tile_lo;
+  auto tile_of = [&](int w) { return w < keep_tiles ? w : tile_lo + (w - keep_tiles); };
   const int per_split = (n_tiles + da.splits - 1) / da.splits;
-  const int tile_begin = tile_lo + split * per_split, tile_end = min(tile_lo + n_tiles, tile_begin + per_split);
+  const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);     // places in the walk
   const int* pages = a.page_ids + a.page_start[seq];
   constexpr int RS = DV + 2;
   if (tile_begin >= tile_end) {
@@ -319,7 +330,7 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
 
   auto issue = [&](int tile) {
     uint8_t* st = smem + (size_t)((tile - tile_begin) % STAGES) * (K_BYTES + V_BYTES);
-    const int page = pages[a.ring_pages > 0 ? tile % a.ring_pages : tile];
+    const int page = pages[page_slot_of_page(tile_of(tile), a.ring_pages)];
     const size_t row0 = ((size_t)page * a.nkv + hk) * KT;
     load_tile<D, ROWB_K>(st, a.k_pool + row0 * D, tid);
     load_tile<DV, ROWB_V>(st + K_BYTES, a.v_pool + row0 * DV, tid);
@@ -331,8 +342,8 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
     __syncthreads();
     const uint8_t* st = smem + (size_t)((tile - tile_begin) % STAGES) * (K_BYTES + V_BYTES);
     const uint32_t k_smem = smem_addr(st), v_smem = k_smem + K_BYTES;
-    const int kbase = tile * KT + warp * 16;        // this warp's 16 keys
-    if (kbase <= pos && kbase + 15 >= first_key) {
+    const int kbase = tile_of(tile) * KT + warp * 16;        // this warp's 16 keys
+    if (kbase <= pos && (kbase + 15 >= first_key || kbase < a.keep)) {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -347,7 +358,7 @@ attention_capped_decode_kernel(CappedDecodeArgs da) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int kj = kbase + i * 8 + (lane & 3) * 2;
-        const bool v0 = kj <= pos && kj >= first_key, v1 = kj + 1 <= pos && kj + 1 >= first_key;
+        const bool v0 = kj <= pos && (kj >= first_key || kj < a.keep), v1 = kj + 1 <= pos && (kj + 1 >= first_key || kj + 1 < a.keep);
         s[i][0] = v0 ? shape_score(s[i][0], a.scale, a.softcap, two_over_cap) : -INFINITY;
         s[i][1] = v1 ? shape_score(s[i][1], a.scale, a.softcap, two_over_cap) : -INFINITY;
         s[i][2] = v0 ? shape_score(s[i][2], a.scale, a.softcap, two_over_cap) : -INFINITY;
@@ -472,7 +483,7 @@ extern "C" int odi_attention_capped_decode(const CappedAttnArgs* args, float* pa
   da.base = *args;
   const CappedAttnArgs& a = da.base;
   if (a.n_seqs <= 0) return 0;
-  if (a.nkv <= 0 || a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.window < 0 || a.ring_pages < 0 || splits < 1) return ODI_ERR_UNSUPPORTED;
+  if (a.nkv <= 0 || a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.window < 0 || a.ring_pages < 0 || a.keep < 0 || splits < 1) return ODI_ERR_UNSUPPORTED;
   if (((uintptr_t)a.q | (uintptr_t)a.k_pool | (uintptr_t)a.v_pool | (uintptr_t)a.out) % 16 != 0) return ODI_ERR_UNSUPPORTED;
   if (splits > 1 && partial == nullptr) return ODI_ERR_ARGUMENT;
   da.partial = partial;
@@ -502,7 +513,7 @@ extern "C" int odi_attention_capped_dims(int* d, int* dv) { *d = D; *dv = DV; re
 extern "C" int odi_attention_capped(const CappedAttnArgs* args, int max_q_len, cudaStream_t stream) {
   const CappedAttnArgs a = *args;
   if (a.n_seqs <= 0 || max_q_len <= 0) return 0;
-  if (a.nkv <= 0 || a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.window < 0 || a.ring_pages < 0) return ODI_ERR_UNSUPPORTED;
+  if (a.nkv <= 0 || a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.window < 0 || a.ring_pages < 0 || a.keep < 0) return ODI_ERR_UNSUPPORTED;
   if (((uintptr_t)a.q | (uintptr_t)a.k_pool | (uintptr_t)a.v_pool | (uintptr_t)a.out) % 16 != 0) return ODI_ERR_UNSUPPORTED;
   const int q_tiles = (max_q_len + 63) / 64;
   if (q_tiles > 65535) return ODI_ERR_UNSUPPORTED;

@@ -10,7 +10,8 @@
 // the key range is split, one split.  Keys are streamed 32 at a time through shared
 // memory (converted to fp32); each warp owns 4 rows; lane j scores key j of the tile;
 // the softmax is the running-maximum form in fp32; the output accumulates in fp32.
-// Key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window).
+// Key j is visible to the query at position p iff j <= p and (window == 0 or j > p - window or j < keep):
+// with keep > 0 a windowed layer goes on seeing the first `keep` positions of its sequence.
 // With softcap c > 0 a score s (already times scale) becomes c tanh(s / c) before the softmax.
 // With sink = 1 the softmax has one more term, of score 0 and without a value: p_j = e^(s_j) / (1 + sum e^(s_k)).
 //
@@ -57,6 +58,7 @@ struct AttnArgs {
   int n_seqs, nq, nkv, page_size, ring_pages, window, splits, bq, head_chunks;
   float scale, softcap;
   int sink;             // 1: the softmax has one more term of score 0 and no value (one is added to its denominator)
+  int keep;             // > 0 with a window: keys 0..keep-1 stay visible beyond the window
 };
 
 // 1 / (l + e^-m) for sums l taken relative to the maximum m: the denominator with the sink's term, without overflow.
@@ -95,7 +97,9 @@ attention_simt_kernel(AttnArgs a) {
   // Key range seen by any row of the tile, cut into tiles of KT, then into splits.
   int k_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
   k_lo = (k_lo / KT) * KT;
-  const int n_tiles = (pos_hi + 1 - k_lo + KT - 1) / KT;
+  // the tiles of kept first keys that lie in front of the window's first tile come first in the walk
+  const int keep_tiles = a.window > 0 && a.keep > 0 ? min((a.keep + KT - 1) / KT, k_lo / KT) : 0;
+  const int n_tiles = keep_tiles + (pos_hi + 1 - k_lo + KT - 1) / KT;
   const int per_split = (n_tiles + a.splits - 1) / a.splits;
   const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
 
@@ -124,7 +128,7 @@ attention_simt_kernel(AttnArgs a) {
 
   const int* pages = a.page_ids + a.page_start[seq];
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int kbase = k_lo + tile * KT;
+    const int kbase = tile < keep_tiles ? tile * KT : k_lo + (tile - keep_tiles) * KT;
     __syncthreads();  // previous tile fully consumed (also orders the Qs writes)
     // All KT keys of a tile lie in one page (page_size is a multiple of KT).
     const int page = pages[page_slot_of(kbase, a.page_size, a.ring_pages)];
@@ -186,7 +190,7 @@ attention_simt_kernel(AttnArgs a) {
     float* prow = Ps + (warp * RW) * KT;
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
-      const bool vis = rpos[r] >= 0 && kj <= rpos[r] && (a.window == 0 || kj > rpos[r] - a.window);
+      const bool vis = rpos[r] >= 0 && kj <= rpos[r] && (a.window == 0 || kj > rpos[r] - a.window || kj < a.keep);
       float sc = s[r] * a.scale;
       if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
       if (!vis) sc = -INFINITY;
@@ -287,7 +291,7 @@ extern "C" int odi_attention_simt(const AttnArgs* args, int max_q_len, int n_tok
                                   cudaStream_t stream) {
   AttnArgs a = *args;
   if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (a.nq % a.nkv != 0 || a.page_size % KT != 0 || a.splits < 1 || a.n_seqs > 65535)
+  if (a.nq % a.nkv != 0 || a.page_size % KT != 0 || a.splits < 1 || a.n_seqs > 65535 || a.keep < 0)
     return ODI_ERR_UNSUPPORTED;
   const int g = a.nq / a.nkv;
   const int hpb = g < 16 ? g : 16;

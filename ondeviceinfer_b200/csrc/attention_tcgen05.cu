@@ -408,7 +408,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       auto load_page = [&](int j, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
         const int s = j % RING;
         if (!mbar_wait(empty + 8 * s, ((uint32_t)(j / RING) & 1u) ^ 1u, abort_ptr)) { ok = false; return; }
-        const int entry = a.ring_pages > 0 ? (tile_lo + j) % a.ring_pages : tile_lo + j;
+        const int entry = page_slot_of_page(tile_lo + j, a.ring_pages);
         const int row = (pages[entry] * a.nkv + hk) * BNK;
         mbar_expect_tx(full + 8 * s, KV_BYTES);
         for (int kb = 0; kb < KB; ++kb)

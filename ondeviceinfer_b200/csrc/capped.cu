@@ -2,9 +2,10 @@
 // around blocks that norm a sublayer's output before adding it:
 //
 //  * rot_unit_prep: per (token, head) the rotation of neighbouring-lane pairs over the first rot_dim lanes, the
-//    division by sqrt(mean of squares + eps), and the write of q to the query buffer, k and v to their cache pages
-//    (v has a width of its own);
-//  * activation: out = act(x), act the exact (erf) GELU or its tanh form, fp32 arithmetic, one rounding;
+//    division by sqrt(mean of squares + eps), optionally times a weight per lane (one for all query heads, one for
+//    all key heads), and the write of q to the query buffer, k and v to their cache pages (v has a width of its own);
+//  * activation: out = act(x), act the exact (erf) GELU, its tanh form or the square of max(x, 0), fp32 arithmetic,
+//    one rounding;
 //  * softcap: x <- c tanh(x / c) in place on fp32 rows (logits);
 //  * concat_cast: out[t] = [a[t] ; b[t]] of two fp32 streams in the compute dtype;
 //  * rmsnorm_add: h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, all fp32 (the norm after a sublayer and the
@@ -28,6 +29,8 @@ struct RotUnitArgs {
   int d_store;          // lanes of a stored q or k head, >= d; the lanes beyond d are written as zero
   float eps;
   int v_from_k;         // 1: there are no v lanes in `qkv`; the value of a head is its key as projected, before the rotation (dv == d)
+  const float* q_w;     // null, or [d]: after the division every query head is multiplied by it lane by lane
+  const float* k_w;     // the same for the key heads
 };
 
 // One warp per (token, head).  Lane i % 32 holds element i in register i / 32, so the partner of lane 2i
@@ -91,8 +94,12 @@ __global__ void rot_unit_prep_kernel(RotUnitArgs a) {
     for (int r = 0; r < MAXP; ++r) ss += x[r] * x[r];
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+    const float* w = kind == 0 ? a.q_w : a.k_w;
 #pragma unroll
-    for (int r = 0; r < MAXP; ++r) x[r] *= inv;
+    for (int r = 0; r < MAXP; ++r) {
+      const int i = lane + 32 * r;
+      x[r] *= (w != nullptr && i < d) ? inv * w[i] : inv;
+    }
   }
 #pragma unroll
   for (int r = 0; r < MAXP; ++r) {
@@ -163,17 +170,21 @@ __global__ void rot_unit_prep_vec_kernel(RotUnitArgs a, int heads_per_warp) {
       }
     }
     float inv = 1.f;
+    const float* w = nullptr;
     if (a.unit) {
       ss = warp_sum(ss);
       inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+      w = kind == 0 ? a.q_w : a.k_w;
     }
 #pragma unroll
     for (int r = 0; r < MAXP4; ++r) {
       const int i = 4 * lane + 128 * r;
       if (i < d) {
+        float4 f = make_float4(inv, inv, inv, inv);
+        if (w != nullptr) { const float4 wv = *(const float4*)(w + i); f.x *= wv.x; f.y *= wv.y; f.z *= wv.z; f.w *= wv.w; }
         uint2 packed;
-        *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(x[r][0] * inv, x[r][1] * inv);
-        *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(x[r][2] * inv, x[r][3] * inv);
+        *(__nv_bfloat162*)&packed.x = __floats2bfloat162_rn(x[r][0] * f.x, x[r][1] * f.y);
+        *(__nv_bfloat162*)&packed.y = __floats2bfloat162_rn(x[r][2] * f.z, x[r][3] * f.w);
         *(uint2*)(dst + i) = packed;
       }
     }
@@ -184,6 +195,8 @@ extern "C" int odi_rot_unit_prep(const RotUnitArgs* args, int dtype, cudaStream_
   RotUnitArgs a = *args;
   if (a.n_tokens <= 0) return 0;
   if (a.v_from_k && a.dv != a.d) return ODI_ERR_ARGUMENT;
+  if (!a.unit && (a.q_w != nullptr || a.k_w != nullptr)) return ODI_ERR_ARGUMENT;
+  if (((uintptr_t)a.q_w | (uintptr_t)a.k_w) % 16 != 0) return ODI_ERR_UNSUPPORTED;
   if (dtype == 1 && a.d == a.d_store && a.d % 4 == 0 && a.d <= 512 && a.d > 0 && a.dv > 0 && !(a.rot_dim & 1) && a.rot_dim <= a.d &&
       ((uintptr_t)a.qkv | (uintptr_t)a.q_out | (uintptr_t)a.k_pool) % 8 == 0 && (a.v_from_k || (a.nkv * a.dv) % 4 == 0)) {
     const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
@@ -217,6 +230,11 @@ __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
 }
 
+__device__ __forceinline__ float relu_squared(float z) { const float r = fmaxf(z, 0.f); return r * r; }
+__device__ __forceinline__ float activation_of(float z, int kind) {
+  return kind == 0 ? gelu_erf(z) : (kind == 1 ? gelu_tanh(z) : relu_squared(z));
+}
+
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, long n, int kind) {
   pdl_launch_dependents();
@@ -224,7 +242,7 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float z = to_f<T>(x[i]);
-  out[i] = from_f<T>(kind == 0 ? gelu_erf(z) : gelu_tanh(z));
+  out[i] = from_f<T>(activation_of(z, kind));
 }
 
 // Eight bf16 per thread (16-byte loads and stores); n8 = n / 8.
@@ -238,15 +256,15 @@ __global__ void activation_vec_kernel(const uint4* __restrict__ x, uint4* __rest
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float2 f = __bfloat1622float2(h[e]);
-    h[e] = kind == 0 ? __floats2bfloat162_rn(gelu_erf(f.x), gelu_erf(f.y)) : __floats2bfloat162_rn(gelu_tanh(f.x), gelu_tanh(f.y));
+    h[e] = __floats2bfloat162_rn(activation_of(f.x, kind), activation_of(f.y, kind));
   }
   out[i] = raw;
 }
 
-// kind: 0 the exact (erf) GELU, 1 its tanh form
+// kind: 0 the exact (erf) GELU, 1 its tanh form, 2 max(x, 0)^2
 extern "C" int odi_activation(const void* x, void* out, long n, int kind, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (kind < 0 || kind > 1) return ODI_ERR_ARGUMENT;
+  if (kind < 0 || kind > 2) return ODI_ERR_ARGUMENT;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == 1 && n % 8 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
     odi_rc = launch_pdl((activation_vec_kernel), dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (const uint4*)x, (uint4*)out, n / 8, kind);

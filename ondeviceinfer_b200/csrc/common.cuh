@@ -144,7 +144,16 @@ __device__ __forceinline__ int merge_used_splits(const int* plan, int splits, in
 
 // Position of key `pos` inside a sequence's page list.  A group that keeps every key
 // has ring_pages == 0; a windowed group keeps a ring of ring_pages pages per sequence.
+// A windowed group that also keeps a sequence's first positions for good puts the pages of those
+// positions in front of the ring: `ring_pages` then carries both numbers, pinned * 65536 + ring, the
+// first `pinned` pages of a sequence are entries 0..pinned-1 of its list and page p >= pinned is entry
+// pinned + (p - pinned) % ring.
+#define ODI_RING_PINNED_SHIFT 16
+__device__ __forceinline__ int page_slot_of_page(int p, int ring_pages) {
+  const int ring = ring_pages & ((1 << ODI_RING_PINNED_SHIFT) - 1), pinned = ring_pages >> ODI_RING_PINNED_SHIFT;
+  if (ring == 0 || p < pinned) return p;
+  return pinned + (p - pinned) % ring;
+}
 __device__ __forceinline__ int page_slot_of(int pos, int page_size, int ring_pages) {
-  int p = pos / page_size;
-  return ring_pages > 0 ? p % ring_pages : p;
+  return page_slot_of_page(pos / page_size, ring_pages);
 }

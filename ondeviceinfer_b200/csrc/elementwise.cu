@@ -28,6 +28,38 @@ extern "C" int odi_embed(const void* table, const int* ids, float* hidden, int n
 }
 
 // ---------------------------------------------------------------------------------
+// Embedding with a factor and absolute sinusoidal positions, all in fp32:
+// hidden[t, j] = table[ids[t], j] * scale + (j even ? sin : cos)(pos[t] * inv_freq[j / 2]).
+// The frequencies come from the host (computed in double, rounded once); the angle is the fp32 product of
+// the position and the frequency, reduced by the full-range sincosf.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ pos,
+                                      const float* __restrict__ inv_freq, float* __restrict__ hidden, int H, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* row = table + (size_t)ids[t] * H;
+  float* out = hidden + (size_t)t * H;
+  const float p = (float)pos[t];
+  for (int i = threadIdx.x; i < (H + 1) / 2; i += blockDim.x) {
+    float sn, cs;
+    sincosf(p * inv_freq[i], &sn, &cs);
+    out[2 * i] = fmaf(to_f<T>(row[2 * i]), scale, sn);
+    if (2 * i + 1 < H) out[2 * i + 1] = fmaf(to_f<T>(row[2 * i + 1]), scale, cs);
+  }
+}
+
+extern "C" int odi_embed_sinusoid(const void* table, const int* ids, const int* pos, const float* inv_freq, float* hidden,
+                                  int n, int H, float scale, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 2048 ? 256 : 128;
+  if (dtype == 0) odi_rc = launch_pdl((embed_sinusoid_kernel<float>), dim3(n), dim3(threads), 0, stream, (const float*)table, ids, pos, inv_freq, hidden, H, scale);
+  else odi_rc = launch_pdl((embed_sinusoid_kernel<bf16>), dim3(n), dim3(threads), 0, stream, (const bf16*)table, ids, pos, inv_freq, hidden, H, scale);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
 // RMSNorm over fp32 rows: y = x * rsqrt(mean(x^2) + eps) rounded to T, then
 // out = weight * y rounded to T (the order of the reference: normalise in fp32, cast,
 // scale).  `rows` (optional) gathers input rows, so the final norm runs only on the

@@ -11,7 +11,7 @@
 //
 // Epilogues: 0 store as T, 1 store as fp32, 2 gated and clamped (W_g holds N gate rows then N up rows;
 // g = min(gate, limit), u = clamp(up, -limit, limit), C = g * sigmoid(alpha * g) * (u + 1) as T), 3 the exact
-// (erf) GELU of the sum as T, 4 its tanh form.
+// (erf) GELU of the sum as T, 4 its tanh form, 5 the square of max(sum, 0) as T.
 //
 // Tile: TM rows x 64 features per block of 256 threads, K in slices of 16 or 32 through shared memory (fp32).
 // TM = 64 (4 x 4 outputs a thread) or 16 (1 x 4), chosen by the caller from the rows a group has; for groups
@@ -26,6 +26,7 @@
 __device__ __forceinline__ float grouped_act(float z, int epi) {
   if (epi == 3) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
   if (epi == 4) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (epi == 5) { const float r = fmaxf(z, 0.f); return r * r; }
   return z;
 }
 
@@ -471,7 +472,7 @@ extern "C" int odi_grouped_gemm_takes_few_rows(const GroupedArgs* args) {
 extern "C" int odi_grouped_gemm(const GroupedArgs* args, int max_tiles, int tm, int dtype, cudaStream_t stream) {
   const GroupedArgs a = *args;
   if (a.N <= 0 || a.groups <= 0) return 0;
-  if (a.K <= 0 || (tm != GV_ROWS && tm != 16 && tm != 64) || a.epi < 0 || a.epi > 4) return ODI_ERR_ARGUMENT;
+  if (a.K <= 0 || (tm != GV_ROWS && tm != 16 && tm != 64) || a.epi < 0 || a.epi > 5) return ODI_ERR_ARGUMENT;
   if (tm == GV_ROWS) {
     if (!odi_grouped_gemm_takes_few_rows(args)) return ODI_ERR_UNSUPPORTED;
     dim3 grid;

@@ -236,9 +236,10 @@ extern "C" int odi_slice_norm(const void* in, const float* w, void* out, int row
 // lanes (>= dv; the ones beyond are left as they are), rows of `gate` are ld lanes apart.  The sigmoid and the
 // product in fp32, one rounding.
 // ---------------------------------------------------------------------------------
+// per_head: the gate has one lane per head (at col + h) that multiplies all of the head's lanes.
 template <typename T>
 __global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate, long total, int heads, int dv, int lanes,
-                                  int ld, int col) {
+                                  int ld, int col, int per_head) {
   pdl_launch_dependents();
   pdl_wait();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -246,7 +247,7 @@ __global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate,
   const int i = (int)(idx % dv);
   const int h = (int)((idx / dv) % heads);
   const long t = idx / ((long)dv * heads);
-  const float gv = to_f<T>(gate[t * ld + col + h * dv + i]);
+  const float gv = to_f<T>(gate[t * ld + col + (per_head ? h : h * dv + i)]);
   T* p = x + (t * heads + h) * lanes + i;
   *p = from_f<T>(to_f<T>(*p) / (1.0f + expf(-gv)));
 }
@@ -276,11 +277,11 @@ __global__ void gate_heads_vec_kernel(bf16* __restrict__ x, const bf16* __restri
 }
 
 extern "C" int odi_gate_heads(void* x, const void* gate, int rows, int heads, int dv, int lanes, int ld, int col,
-                              int dtype, cudaStream_t stream) {
+                              int per_head, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (heads <= 0 || dv <= 0 || lanes < dv || col < 0 || col + heads * dv > ld) return ODI_ERR_ARGUMENT;
+  if (heads <= 0 || dv <= 0 || lanes < dv || col < 0 || col + heads * (per_head ? 1 : dv) > ld) return ODI_ERR_ARGUMENT;
   const long total = (long)rows * heads * dv;
-  if (dtype == 1 && dv % 8 == 0 && lanes % 8 == 0 && ld % 8 == 0 && col % 8 == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0) {
+  if (!per_head && dtype == 1 && dv % 8 == 0 && lanes % 8 == 0 && ld % 8 == 0 && col % 8 == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0) {
     const long total8 = total / 8, vblocks = (total8 + 255) / 256;
     if (vblocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
     odi_rc = launch_pdl((gate_heads_vec_kernel), dim3((unsigned)vblocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, total8, heads, dv, lanes, ld, col);
@@ -288,7 +289,7 @@ extern "C" int odi_gate_heads(void* x, const void* gate, int rows, int heads, in
   }
   const long blocks = (total + 255) / 256;
   if (blocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
-  if (dtype == 0) odi_rc = launch_pdl((gate_heads_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, total, heads, dv, lanes, ld, col);
-  else odi_rc = launch_pdl((gate_heads_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, total, heads, dv, lanes, ld, col);
+  if (dtype == 0) odi_rc = launch_pdl((gate_heads_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, total, heads, dv, lanes, ld, col, per_head);
+  else odi_rc = launch_pdl((gate_heads_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, total, heads, dv, lanes, ld, col, per_head);
   return launch_status();
 }

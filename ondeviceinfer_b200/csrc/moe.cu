@@ -1,7 +1,8 @@
 // Routing of a mixture of experts and the bookkeeping around its grouped products.  Everything here is fp32
 // and integer work; nothing waits for the host, so a step with routed experts can be captured in a graph.
 //
-//  route    per token: scores s = softmax(logits) over all router outputs; choice scores c = s + correction;
+//  route    per token: scores s = softmax(logits) over all router outputs (or, with `sigmoid`, s_e = 1 / (1 + e^-z_e),
+//           each output for itself); choice scores c = s + correction;
 //           the router outputs form `n_groups` equal groups of neighbours, a group's score is its largest c,
 //           only members of the `keep` best groups may be chosen; the `top` largest c among them are chosen
 //           (ties: the lower index); the weight of a chosen output is its s (no renormalisation).
@@ -24,6 +25,7 @@ struct RouteArgs {
   int* ids;                 // [n_tokens, top]
   float* weights;           // [n_tokens, top]
   int n_tokens, n_all, n_groups, keep, top;
+  int sigmoid;              // 1: the score of an output is the logistic function of its logit, not the softmax
 };
 
 // (value, index) with "larger value, then lower index" as the order
@@ -49,14 +51,19 @@ moe_route_kernel(RouteArgs a) {
   float* c = s + a.n_all;
   float* gs = c + a.n_all;
   const float* z = a.logits + (size_t)t * a.n_all;
-  float m = -INFINITY;
-  for (int e = lane; e < a.n_all; e += 32) m = fmaxf(m, z[e]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < a.n_all; e += 32) { const float p = expf(z[e] - m); s[e] = p; sum += p; }
-  sum = warp_sum(sum);
+  float sum = 1.f;
+  if (a.sigmoid) {
+    for (int e = lane; e < a.n_all; e += 32) s[e] = 1.0f / (1.0f + expf(-z[e]));
+  } else {
+    float m = -INFINITY;
+    for (int e = lane; e < a.n_all; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    sum = 0.f;
+    for (int e = lane; e < a.n_all; e += 32) { const float p = expf(z[e] - m); s[e] = p; sum += p; }
+    sum = warp_sum(sum);
+  }
   for (int e = lane; e < a.n_all; e += 32) {
-    s[e] = s[e] / sum;
+    if (!a.sigmoid) s[e] = s[e] / sum;
     c[e] = s[e] + (a.correction != nullptr ? a.correction[e] : 0.f);
   }
   __syncwarp();
@@ -293,7 +300,7 @@ struct CombineArgs {
   const void* expert_out;   // [n_pairs, H] rows in the sorted order: fp32, or T if out_is_t
   const void* input;      // [n_tokens, H] in T: what identity outputs pass on
   const int* ids;
-  const float* weights;
+  const float* weights;   // null: every chosen row counts once (the weights were applied elsewhere)
   const int* pos;
   int n_tokens, H, top, n_experts, out_is_t;
   int assign;             // the sums replace the rows of `residual` instead of being added to them
@@ -314,7 +321,7 @@ __global__ void moe_combine_kernel(CombineArgs a) {
       if (e >= a.n_experts) v = to_f<T>(((const T*)a.input)[(size_t)t * a.H + i]);
       else if (a.out_is_t) v = to_f<T>(((const T*)a.expert_out)[(size_t)a.pos[p] * a.H + i]);
       else v = ((const float*)a.expert_out)[(size_t)a.pos[p] * a.H + i];
-      sum = fmaf(a.weights[p], v, sum);
+      sum = fmaf(a.weights != nullptr ? a.weights[p] : 1.f, v, sum);
     }
     if (a.assign) a.residual[(size_t)t * a.H + i] = sum;
     else a.residual[(size_t)t * a.H + i] += sum;
@@ -345,7 +352,7 @@ __global__ void moe_combine_vec_kernel(CombineArgs a) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
       }
-      const float w = a.weights[p];
+      const float w = a.weights != nullptr ? a.weights[p] : 1.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) sum[j] = fmaf(w, v[j], sum[j]);
     }
@@ -375,16 +382,23 @@ extern "C" int odi_moe_combine(const CombineArgs* args, int dtype, cudaStream_t 
   return launch_status();
 }
 
-// Rows of the routed tokens' inputs in the sorted order: out[i] = x[perm[i] / top] for the places that are taken.
+// Rows of the routed tokens' inputs in the sorted order: out[i] = x[perm[i] / top] for the places that are taken;
+// with `weights` ([tokens, top], fp32) the row is multiplied by the weight of its (token, choice) pair, in fp32,
+// and rounded once (experts whose weight multiplies their input).
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ offsets,
-                                  T* __restrict__ out, int H, int top, int n_experts) {
+                                  T* __restrict__ out, int H, int top, int n_experts, const float* __restrict__ weights) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x;
   if (i >= offsets[n_experts]) return;
   const T* src = x + (size_t)(perm[i] / top) * H;
   T* dst = out + (size_t)i * H;
+  if (weights != nullptr) {
+    const float w = weights[perm[i]];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = from_f<T>(w * to_f<T>(src[c]));
+    return;
+  }
   for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
 }
 
@@ -401,16 +415,16 @@ __global__ void moe_gather_vec_kernel(const uint4* __restrict__ x, const int* __
 }
 
 extern "C" int odi_moe_gather(const void* x, const int* perm, const int* offsets, void* out, int n_pairs, int H, int top,
-                              int n_experts, int dtype, cudaStream_t stream) {
+                              int n_experts, const float* weights, int dtype, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   const size_t row_bytes = (size_t)H * (dtype == 0 ? 4 : 2);
-  if (row_bytes % 16 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+  if (weights == nullptr && row_bytes % 16 == 0 && ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
     const int row16 = (int)(row_bytes / 16);
     odi_rc = launch_pdl(moe_gather_vec_kernel, dim3(n_pairs), dim3(row16 >= 256 ? 256 : 128), 0, stream, (const uint4*)x, perm, offsets, (uint4*)out, row16, top, n_experts);
     return launch_status();
   }
-  if (dtype == 0) odi_rc = launch_pdl((moe_gather_kernel<float>), dim3(n_pairs), dim3(128), 0, stream, (const float*)x, perm, offsets, (float*)out, H, top, n_experts);
-  else odi_rc = launch_pdl((moe_gather_kernel<bf16>), dim3(n_pairs), dim3(128), 0, stream, (const bf16*)x, perm, offsets, (bf16*)out, H, top, n_experts);
+  if (dtype == 0) odi_rc = launch_pdl((moe_gather_kernel<float>), dim3(n_pairs), dim3(128), 0, stream, (const float*)x, perm, offsets, (float*)out, H, top, n_experts, weights);
+  else odi_rc = launch_pdl((moe_gather_kernel<bf16>), dim3(n_pairs), dim3(128), 0, stream, (const bf16*)x, perm, offsets, (bf16*)out, H, top, n_experts, weights);
   return launch_status();
 }
 

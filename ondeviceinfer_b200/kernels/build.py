@@ -165,6 +165,8 @@ ALL_SOURCES = {
     "latent": [{}],
     "capped": [{}],
     "parallel": [{}],
+    "scaled_block": [{}],
+    "ssd": [{}],
     "attention_capped_mma": [{"ODI_HEAD_DIM": 128, "ODI_VALUE_DIM": 128}],
     "attention_latent_mma": [{"ODI_HEAD_DIM": 576, "ODI_VALUE_DIM": 512}],      # a latent cache, on the tensor cores
     "grouped_gemm": [{}],

@@ -97,6 +97,22 @@ def embed(table: torch.Tensor, ids: torch.Tensor, hidden: torch.Tensor) -> None:
                          c_int(dtype_code(table.dtype)), _stream()), "embed")
 
 
+def embed_sinusoid(table: torch.Tensor, ids: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, hidden: torch.Tensor,
+                   scale: float) -> None:
+    """hidden[t, j] = table[ids[t], j] * scale + (sin for even j, cos for odd j)(pos[t] * inv_freq[j // 2]), fp32."""
+    _require(table, "table", ndim=2)
+    _require(ids, "ids", torch.int32, 1)
+    _require(pos, "pos", torch.int32, 1)
+    _require(inv_freq, "inv_freq", torch.float32, 1)
+    _require(hidden, "hidden", torch.float32, 2)
+    H = table.shape[1]
+    if hidden.shape != (ids.numel(), H) or pos.numel() != ids.numel() or inv_freq.numel() != (H + 1) // 2:
+        raise KernelError(f"embed_sinusoid sizes disagree: hidden {tuple(hidden.shape)}, table {tuple(table.shape)}")
+    lib = load_library("elementwise")
+    _check(lib.odi_embed_sinusoid(_ptr(table), _ptr(ids), _ptr(pos), _ptr(inv_freq), _ptr(hidden), c_int(ids.numel()),
+                                  c_int(H), c_float(scale), c_int(dtype_code(table.dtype)), _stream()), "embed_sinusoid")
+
+
 def rmsnorm_adds(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: torch.Tensor) -> bool:
     """Whether :func:`rmsnorm` can take ``add`` for these tensors (the vector form: a width that is a multiple of 4
     and at most 8,192, aligned tensors, ``add`` in the dtype of ``out``)."""
@@ -575,7 +591,7 @@ class _AttnArgs(Structure):
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("page_size", c_int),
                 ("ring_pages", c_int), ("window", c_int), ("splits", c_int), ("bq", c_int),
-                ("head_chunks", c_int), ("scale", c_float), ("softcap", c_float), ("sink", c_int)]
+                ("head_chunks", c_int), ("scale", c_float), ("softcap", c_float), ("sink", c_int), ("keep", c_int)]
 
 
 SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
@@ -584,10 +600,11 @@ SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
 def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                    nq: int, nkv: int, d: int, page_size: int, ring_pages: int, window: int, scale: float,
                    splits: int = 1, partial: Optional[torch.Tensor] = None, dv: Optional[int] = None,
-                   shared_kv: bool = False, softcap: float = 0.0, sink: bool = False) -> None:
+                   shared_kv: bool = False, softcap: float = 0.0, sink: bool = False, keep: int = 0) -> None:
     """Causal GQA over the paged cache for any mixture of prompt and decode sequences.  ``softcap`` c > 0:
     scores (times ``scale``) become c tanh(score / c) before the softmax.  ``sink``: the softmax has one more
-    term of score 0 and no value, p_j = exp(s_j) / (1 + sum_k exp(s_k)).
+    term of score 0 and no value, p_j = exp(s_j) / (1 + sum_k exp(s_k)).  ``keep`` > 0 with a window: the first
+    ``keep`` positions of a sequence stay visible beyond the window (a ring then has their pages pinned in front).
 
     ``dv`` (default ``d``): width of the value rows and of the output.  ``shared_kv``: a cached row is key and
     value at once (the value is its first ``dv`` lanes; ``v_pool`` is None), as in attention over a latent
@@ -616,7 +633,7 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _AttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                      _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, page_size, ring_pages, window, splits,
-                     0, 0, scale, softcap, 1 if sink else 0)
+                     0, 0, scale, softcap, 1 if sink else 0, keep)
     defines = {"ODI_HEAD_DIM": d}
     if not plain:
         defines.update({"ODI_VALUE_DIM": dv, "ODI_SHARED_KV": 1 if shared_kv else 0})
@@ -945,13 +962,15 @@ def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, nor
                 tok_seq, tok_pos, page_start, page_ids, *, heads: int, d: int, r: int, R: int, rot_dims: int,
                 interleaved: bool, page_size: int, ring_pages: int, write_cache: bool, eps: float,
                 latent_out: Optional[torch.Tensor] = None, key_rot_out: Optional[torch.Tensor] = None,
-                row: Optional[int] = None, down: Optional[torch.Tensor] = None, has_down: bool = True) -> None:
+                row: Optional[int] = None, down: Optional[torch.Tensor] = None, has_down: bool = True,
+                trailing: int = 0) -> None:
     """From the fused query / down projection ``proj`` [tokens, heads (d + r) + R + r]: the normed latent and the
     rotated shared key lanes into the token's cache row, each head's rotated query lanes into lanes R.. of
     ``q_abs`` [tokens, heads, row] (see ``csrc/latent.cu``).  ``row`` (default R + r) is the width of a cache row and
     of a head's absorbed query; lanes beyond R + r are left as they are (zero).  With ``down`` ([tokens, >= R + r],
     the down projection in its first lanes) ``proj`` holds the queries only; ``has_down`` False (a layer that reads
-    another layer's cache rows) prepares the queries and nothing else."""
+    another layer's cache rows) prepares the queries and nothing else.  ``trailing``: lanes of ``proj`` behind all
+    of these that belong to somebody else (a gate computed by the same product)."""
     row = R + r if row is None else row
     _require(proj, "proj", ndim=2)
     _require(q_abs, "q_abs", proj.dtype)
@@ -968,7 +987,7 @@ def latent_prep(proj: torch.Tensor, q_abs: torch.Tensor, pool: torch.Tensor, nor
         _require(down, "down", proj.dtype, 2)
         if down.shape[0] != n or down.shape[1] < R + r:
             raise KernelError("latent_prep: down is [tokens, >= R + r]")
-    if (proj.shape[1] != heads * (d + r) + (0 if apart else R + r) or q_abs.numel() != n * heads * row or row < R + r):
+    if (proj.shape[1] != heads * (d + r) + (0 if apart else R + r) + trailing or trailing < 0 or q_abs.numel() != n * heads * row or row < R + r):
         raise KernelError("latent_prep sizes disagree")
     if rot_dims > 0:
         _require(cos_t, "cos_t", torch.float32, 2)
@@ -1005,17 +1024,20 @@ def slice_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Ten
                               c_float(eps), c_int(dtype_code(x.dtype)), _stream()), "slice_norm")
 
 
-def gate_heads(x: torch.Tensor, gate: torch.Tensor, *, heads: int, dv: int, lanes: int, col: int = 0) -> None:
+def gate_heads(x: torch.Tensor, gate: torch.Tensor, *, heads: int, dv: int, lanes: int, col: int = 0,
+               per_head: bool = False) -> None:
     """x[t, h, i] *= sigmoid(gate[t, col + h dv + i]) for i < dv, in place; ``x`` is [tokens, heads * lanes]
-    (lanes >= dv; the lanes beyond stay), ``gate`` a product whose rows hold the gate's lanes from ``col`` on."""
+    (lanes >= dv; the lanes beyond stay), ``gate`` a product whose rows hold the gate's lanes from ``col`` on.
+    ``per_head``: the gate has one lane per head, gate[t, col + h], for all of the head's lanes."""
     _require(x, "x", ndim=2)
     _require(gate, "gate", x.dtype, 2)
     n = x.shape[0]
-    if x.shape[1] != heads * lanes or gate.shape[0] != n or lanes < dv or col < 0 or col + heads * dv > gate.shape[1]:
+    if (x.shape[1] != heads * lanes or gate.shape[0] != n or lanes < dv or col < 0
+            or col + heads * (1 if per_head else dv) > gate.shape[1]):
         raise KernelError(f"gate_heads sizes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, heads={heads}, dv={dv}")
     lib = load_library("latent")
     _check(lib.odi_gate_heads(_ptr(x), _ptr(gate), c_int(n), c_int(heads), c_int(dv), c_int(lanes), c_int(gate.shape[1]),
-                              c_int(col), c_int(dtype_code(x.dtype)), _stream()), "gate_heads")
+                              c_int(col), c_int(1 if per_head else 0), c_int(dtype_code(x.dtype)), _stream()), "gate_heads")
 
 
 class _LatentExpandArgs(Structure):
@@ -1056,7 +1078,7 @@ class _GroupedArgs(Structure):
                 ("groups", c_int), ("index_div", c_int), ("epi", c_int), ("limit", c_float), ("alpha", c_float)]
 
 
-GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP, GROUPED_GELU_ERF, GROUPED_GELU_TANH = 0, 1, 2, 3, 4
+GROUPED_STORE, GROUPED_STORE_F32, GROUPED_GATED_CLAMP, GROUPED_GELU_ERF, GROUPED_GELU_TANH, GROUPED_RELU2 = 0, 1, 2, 3, 4, 5
 
 
 FEW_ROWS = 4      # row tile of the grouped product's form for single-token steps (weights through registers only)
@@ -1121,13 +1143,15 @@ def grouped_gemm_routed(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, table
 
 class _RouteArgs(Structure):
     _fields_ = [("logits", c_void_p), ("correction", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
-                ("n_tokens", c_int), ("n_all", c_int), ("n_groups", c_int), ("keep", c_int), ("top", c_int)]
+                ("n_tokens", c_int), ("n_all", c_int), ("n_groups", c_int), ("keep", c_int), ("top", c_int),
+                ("sigmoid", c_int)]
 
 
 def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, *,
-              n_groups: int, keep: int) -> None:
+              n_groups: int, keep: int, sigmoid: bool = False) -> None:
     """Grouped top-k routing of fp32 ``logits`` [tokens, outputs] (see ``csrc/moe.cu``): ``ids`` and ``weights``
-    [tokens, top] receive the chosen outputs, best first, and their softmax scores."""
+    [tokens, top] receive the chosen outputs, best first, and their scores: the softmax over the outputs, or with
+    ``sigmoid`` the logistic function of each logit for itself."""
     _require(logits, "logits", torch.float32, 2)
     _require(ids, "ids", torch.int32, 2)
     _require(weights, "weights", torch.float32, 2)
@@ -1138,7 +1162,8 @@ def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], ids: tor
         _require(correction, "correction", torch.float32, 1)
         if correction.numel() != n_all:
             raise KernelError("the correction has one entry per router output")
-    args = _RouteArgs(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, n_all, n_groups, keep, ids.shape[1])
+    args = _RouteArgs(_ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, n_all, n_groups, keep, ids.shape[1],
+                      1 if sigmoid else 0)
     lib = load_library("moe")
     _check(lib.odi_moe_route(byref(args), _stream()), "moe_route")
 
@@ -1177,16 +1202,21 @@ def moe_group(ids: torch.Tensor, counts: torch.Tensor, table: RoutingTable) -> N
     _check(lib.odi_moe_group(byref(args), _stream()), "moe_group", 1 if table.n_pairs <= 2048 and table.n_experts <= 4096 else 3)
 
 
-def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor) -> None:
-    """out[i] = x[perm[i] // top] for every taken place i of ``table``'s sorted order (other rows are left alone)."""
+def moe_gather(x: torch.Tensor, table: RoutingTable, out: torch.Tensor, weights: Optional[torch.Tensor] = None) -> None:
+    """out[i] = x[perm[i] // top] for every taken place i of ``table``'s sorted order (other rows are left alone);
+    with ``weights`` (fp32 [tokens, top]) the row is multiplied by the weight of its (token, choice) pair."""
     _require(x, "x", ndim=2)
     _require(out, "out", x.dtype, 2)
     if out.shape != (table.n_pairs, x.shape[1]):
         raise KernelError("moe_gather sizes disagree")
+    if weights is not None:
+        _require(weights, "weights", torch.float32, 2)
+        if weights.numel() != table.n_pairs:
+            raise KernelError("moe_gather: one weight per (token, choice) pair")
     lib = load_library("moe")
     _check(lib.odi_moe_gather(_ptr(x), _ptr(table.perm), _ptr(table.offsets), _ptr(out), c_int(table.n_pairs),
-                              c_int(x.shape[1]), c_int(table.top), c_int(table.n_experts), c_int(dtype_code(x.dtype)),
-                              _stream()), "moe_gather")
+                              c_int(x.shape[1]), c_int(table.top), c_int(table.n_experts), _ptr(weights),
+                              c_int(dtype_code(x.dtype)), _stream()), "moe_gather")
 
 
 class _CombineArgs(Structure):
@@ -1196,8 +1226,9 @@ class _CombineArgs(Structure):
 
 
 def moe_combine(residual: torch.Tensor, expert_out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor,
-                weights: torch.Tensor, table: RoutingTable, assign: bool = False) -> None:
-    """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output).
+                weights: Optional[torch.Tensor], table: RoutingTable, assign: bool = False) -> None:
+    """residual[t] += sum_k weights[t, k] * (row pos[t, k] of ``expert_out``, or ``x[t]`` for an identity output);
+    ``weights`` None: every chosen row counts once.
     ``expert_out`` is fp32, or in the dtype of ``x``.  ``assign``: the sums replace the rows of ``residual``."""
     _require(residual, "residual", torch.float32, 2)
     _require(expert_out, "expert_out", ndim=2)
@@ -1237,19 +1268,28 @@ class _RotUnitArgs(Structure):
                 ("cos_t", c_void_p), ("sin_t", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p),
                 ("page_start", c_void_p), ("page_ids", c_void_p), ("n_tokens", c_int), ("nq", c_int), ("nkv", c_int),
                 ("d", c_int), ("dv", c_int), ("rot_dim", c_int), ("page_size", c_int), ("ring_pages", c_int),
-                ("write_kv", c_int), ("unit", c_int), ("d_store", c_int), ("eps", c_float), ("v_from_k", c_int)]
+                ("write_kv", c_int), ("unit", c_int), ("d_store", c_int), ("eps", c_float), ("v_from_k", c_int),
+                ("q_w", c_void_p), ("k_w", c_void_p)]
 
 
 def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, page_start, page_ids, *, nq: int,
                   nkv: int, d: int, dv: int, rot_dim: int, page_size: int, ring_pages: int, write_kv: bool,
-                  unit_eps: Optional[float], d_store: Optional[int] = None, v_from_k: bool = False) -> None:
+                  unit_eps: Optional[float], d_store: Optional[int] = None, v_from_k: bool = False,
+                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None) -> None:
     """Head preparation of an attention that rotates first and norms afterwards: q and k heads (``d`` lanes) of
     ``qkv`` [tokens, nq d + nkv d + nkv dv] are rotated over their first ``rot_dim`` lanes (lane 2i with 2i + 1;
     ``cos_t`` None: not at all) and, with ``unit_eps`` not None, divided by sqrt(mean of squares + eps); q goes to
     ``q_out``, k and the v heads (``dv`` lanes, as they are) to the token's row of their cache pages.  Stored q
     and k heads have ``d_store`` >= ``d`` lanes (default ``d``), the ones beyond ``d`` zero.  ``v_from_k``: ``qkv``
-    holds no v lanes ([tokens, nq d + nkv d]); the value of a head is its key as projected, before the rotation."""
+    holds no v lanes ([tokens, nq d + nkv d]); the value of a head is its key as projected, before the rotation.
+    ``q_weight`` / ``k_weight`` (fp32 [d], with ``unit_eps``): after the division every query resp. key head is
+    multiplied by it lane by lane (an RMS norm per head with a weight that the heads share)."""
     d_store = d if d_store is None else d_store
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _require(w, name, torch.float32, 1)
+            if w.numel() != d or unit_eps is None:
+                raise KernelError(f"{name} has one entry per lane of a head and goes with unit_eps")
     if v_from_k and dv != d:
         raise KernelError("values that are the keys have the keys' width")
     _require(qkv, "qkv", ndim=2)
@@ -1271,7 +1311,7 @@ def rot_unit_prep(qkv, q_out, k_pool, v_pool, cos_t, sin_t, tok_seq, tok_pos, pa
     args = _RotUnitArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq),
                         _ptr(tok_pos), _ptr(page_start), _ptr(page_ids), n, nq, nkv, d, dv, rot_dim, page_size, ring_pages,
                         1 if write_kv else 0, 0 if unit_eps is None else 1, d_store, 0.0 if unit_eps is None else unit_eps,
-                        1 if v_from_k else 0)
+                        1 if v_from_k else 0, _ptr(q_weight), _ptr(k_weight))
     lib = load_library("capped")
     _check(lib.odi_rot_unit_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "rot_unit_prep")
 
@@ -1280,7 +1320,7 @@ class _CappedAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p), ("cu_q", c_void_p),
                 ("past", c_void_p), ("page_start", c_void_p), ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int),
                 ("nkv", c_int), ("ring_pages", c_int), ("window", c_int), ("scale", c_float), ("softcap", c_float),
-                ("sink", c_int)]
+                ("sink", c_int), ("keep", c_int)]
 
 
 def attention_capped_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
@@ -1290,10 +1330,11 @@ def attention_capped_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
 
 def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int, nq: int,
                      nkv: int, d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
-                     softcap: float = 0.0, sink: bool = False) -> None:
+                     softcap: float = 0.0, sink: bool = False, keep: int = 0) -> None:
     """bf16 causal GQA on the tensor cores with squashed scores (``softcap`` c > 0: c tanh(score / c)), a window
     (0: none; the cache may be a ring of pages) and value rows of ``dv`` lanes, for any mixture of sequences.
-    ``sink``: one more term of score 0 and no value in the softmax."""
+    ``sink``: one more term of score 0 and no value in the softmax.  ``keep`` > 0 with a window: the first ``keep``
+    positions of a sequence stay visible beyond the window."""
     if not attention_capped_supported(q.dtype, d, dv) or page_size != 64:
         raise KernelError(f"attention_capped takes bfloat16 heads in steps of 16 up to 256 and pages of 64 (d={d}, dv={dv})")
     _require(q, "q", torch.bfloat16)
@@ -1304,7 +1345,7 @@ def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *
     if out.numel() != n_tokens * nq * dv or k_pool.shape[-1] != d or v_pool.shape[-1] != dv:
         raise KernelError("attention_capped sizes disagree")
     args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
-                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0)
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0, keep)
     lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
     _check(lib.odi_attention_capped(byref(args), c_int(max_q_len), _stream()), "attention_capped")
 
@@ -1312,7 +1353,7 @@ def attention_capped(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *
 def attention_capped_decode(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, nq: int, nkv: int,
                             d: int, dv: int, page_size: int, ring_pages: int, window: int, scale: float,
                             softcap: float = 0.0, splits: int = 1, partial: Optional[torch.Tensor] = None,
-                            sink: bool = False) -> None:
+                            sink: bool = False, keep: int = 0) -> None:
     """:func:`attention_capped` for steps in which every sequence brings one token: each sequence's visible keys
     are cut into ``splits`` ranges that blocks of their own take; ``partial`` (fp32, tokens * nq * splits * (dv + 2))
     holds their results for the combine kernel."""
@@ -1329,17 +1370,17 @@ def attention_capped_decode(q, k_pool, v_pool, out, cu_q, past, page_start, page
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _CappedAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start),
-                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0)
+                           _ptr(page_ids), n_seqs, nq, nkv, ring_pages, window, scale, softcap, 1 if sink else 0, keep)
     lib = load_library("attention_capped_mma", {"ODI_HEAD_DIM": d, "ODI_VALUE_DIM": dv})
     _check(lib.odi_attention_capped_decode(byref(args), _ptr(partial), c_int(splits), _stream()), "attention_capped_decode",
            2 if splits > 1 else 1)
 
 
-ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "relu2": 2}      # relu2: the square of max(x, 0)
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
-    """out = act(x) elementwise (fp32 arithmetic, one rounding); ``kind`` "gelu_erf" or "gelu_tanh"."""
+    """out = act(x) elementwise (fp32 arithmetic, one rounding); ``kind`` one of ``ACTIVATIONS``."""
     _require(x, "x")
     _require(out, "out", x.dtype)
     if kind not in ACTIVATIONS or out.numel() != x.numel():
@@ -1601,3 +1642,131 @@ def scaled_add(x: torch.Tensor, y: torch.Tensor, m: float) -> None:
         raise KernelError(f"scaled_add sizes disagree: {tuple(x.shape)} and {tuple(y.shape)}")
     lib = load_library("parallel")
     _check(lib.odi_scaled_add(_ptr(x), _ptr(y), c_long(x.numel()), c_float(m), _stream()), "scaled_add")
+
+
+# ------------------------------------------------------------------------------ block with two norms and scaled outputs
+
+
+def dual_norm(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, eps: float, out1: torch.Tensor, out2: torch.Tensor) -> None:
+    """out1 = cast(x r w1), out2 = cast(x r w2) with r = 1 / sqrt(mean(x^2) + eps) per row: two RMS norms of the same
+    fp32 rows in one pass (``w1``, ``w2``: what multiplies each lane, fp32)."""
+    _require(x, "x", torch.float32, 2)
+    _require(w1, "w1", torch.float32, 1)
+    _require(w2, "w2", torch.float32, 1)
+    _require(out1, "out1", ndim=2)
+    _require(out2, "out2", out1.dtype, 2)
+    n, H = x.shape
+    if w1.numel() != H or w2.numel() != H or out1.shape != (n, H) or out2.shape != (n, H):
+        raise KernelError("dual_norm sizes disagree")
+    lib = load_library("scaled_block")
+    _check(lib.odi_dual_norm(_ptr(x), _ptr(w1), _ptr(w2), _ptr(out1), _ptr(out2), c_int(n), c_int(H), c_float(eps),
+                             c_int(dtype_code(out1.dtype)), _stream()), "dual_norm")
+
+
+def scaled_add2(x: torch.Tensor, a: torch.Tensor, s1: torch.Tensor, b: Optional[torch.Tensor] = None,
+                s2: Optional[torch.Tensor] = None, copy: Optional[torch.Tensor] = None) -> None:
+    """x += a * s1 (+ b * s2) on fp32 rows, ``s1`` and ``s2`` one number per lane; ``copy`` (optional, any compute
+    dtype) receives the new rows once more."""
+    _require(x, "x", torch.float32, 2)
+    _require(a, "a", torch.float32, 2)
+    _require(s1, "s1", torch.float32, 1)
+    n, H = x.shape
+    if a.shape != (n, H) or s1.numel() != H:
+        raise KernelError("scaled_add2 sizes disagree")
+    if b is not None:
+        _require(b, "b", torch.float32, 2)
+        _require(s2, "s2", torch.float32, 1)
+        if b.shape != (n, H) or s2.numel() != H:
+            raise KernelError("scaled_add2 sizes disagree")
+    if copy is not None:
+        _require(copy, "copy", ndim=2)
+        if copy.shape != (n, H):
+            raise KernelError("scaled_add2: the copy has the shape of x")
+    lib = load_library("scaled_block")
+    _check(lib.odi_scaled_add2(_ptr(x), _ptr(a), _ptr(s1), _ptr(b), _ptr(s2), _ptr(copy), c_long(n), c_int(H),
+                               c_int(0 if copy is None else dtype_code(copy.dtype)), _stream()), "scaled_add2")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = cast(x) for fp32 ``x``, into the compute dtype of ``out`` (same shape)."""
+    _require(x, "x", torch.float32)
+    _require(out, "out")
+    if out.shape != x.shape:
+        raise KernelError("cast_rows sizes disagree")
+    lib = load_library("scaled_block")
+    _check(lib.odi_cast_rows(_ptr(x), _ptr(out), c_long(x.numel()), c_int(dtype_code(out.dtype)), _stream()), "cast_rows")
+
+
+def weighted_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ca: float, cb: float) -> None:
+    """out = ca * a + cb * b on fp32 tensors of one shape (``out`` may be ``a`` or ``b``)."""
+    for name, t in (("out", out), ("a", a), ("b", b)):
+        _require(t, name, torch.float32)
+    if a.shape != out.shape or b.shape != out.shape:
+        raise KernelError("weighted_sum sizes disagree")
+    lib = load_library("scaled_block")
+    _check(lib.odi_weighted_sum(_ptr(out), _ptr(a), _ptr(b), c_long(out.numel()), c_float(ca), c_float(cb), _stream()),
+           "weighted_sum")
+
+
+def gated_lookup(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, col: int) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j] for ``z`` and ``out`` [tokens, dim] and ``table``
+    [rows, >= col + dim], all in one compute dtype (fp32 arithmetic, one rounding)."""
+    _require(z, "z", ndim=2)
+    _require(table, "table", z.dtype, 2)
+    _require(ids, "ids", torch.int32, 1)
+    _require(out, "out", z.dtype, 2)
+    n, dim = z.shape
+    if out.shape != (n, dim) or ids.numel() != n or col < 0 or col + dim > table.shape[1]:
+        raise KernelError("gated_lookup sizes disagree")
+    lib = load_library("scaled_block")
+    _check(lib.odi_gated_lookup(_ptr(z), _ptr(table), _ptr(ids), _ptr(out), c_long(n), c_int(dim), c_int(table.shape[1]),
+                                c_int(col), c_int(dtype_code(z.dtype)), _stream()), "gated_lookup")
+
+
+# ------------------------------------------------------------------------------ state-space mixer
+
+
+class _SsdArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("conv_w", c_void_p), ("conv_b", c_void_p), ("dt_bias", c_void_p), ("a_log", c_void_p),
+                ("d_skip", c_void_p), ("norm_w", c_void_p), ("conv_state", c_void_p), ("state", c_void_p), ("xbc", c_void_p),
+                ("y", c_void_p), ("out", c_void_p), ("cu_q", c_void_p), ("tok_seq", c_void_p), ("slots", c_void_p),
+                ("n_tokens", c_int), ("n_seqs", c_int), ("ld", c_int), ("heads", c_int), ("P", c_int), ("N", c_int),
+                ("G", c_int), ("taps", c_int), ("norm_groups", c_int), ("eps", c_float)]
+
+
+SSD_MAX_STATE, SSD_MAX_TAPS = 256, 16
+
+
+def ssd_mix(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+            d_skip: torch.Tensor, norm_w: torch.Tensor, conv_state: Optional[torch.Tensor], state: torch.Tensor,
+            out: torch.Tensor, cu_q, tok_seq, slots, *, n_seqs: int, heads: int, head_dim: int, state_dim: int,
+            groups: int, norm_groups: int, eps: float) -> None:
+    """The state-space mixer between its projections (``csrc/ssd.cu``): ``proj`` [tokens, 2 inner + 2 G N + heads]
+    = [z | x | B | C | dt] in the compute dtype, ``out`` [tokens, inner] in the same; ``conv_state``
+    [slots, taps - 1, inner + 2 G N] and ``state`` [slots, heads, N, P] are fp32 rows of the cache, advanced in place
+    over all tokens that each sequence brings."""
+    _require(proj, "proj", ndim=2)
+    _require(out, "out", proj.dtype, 2)
+    n = proj.shape[0]
+    inner, C = heads * head_dim, heads * head_dim + 2 * groups * state_dim
+    taps = conv_w.shape[1]
+    for name, t, shape in (("conv_w", conv_w, (C, taps)), ("conv_b", conv_b, (C,)), ("dt_bias", dt_bias, (heads,)),
+                           ("a_log", a_log, (heads,)), ("d_skip", d_skip, (heads,)), ("norm_w", norm_w, (inner,))):
+        _require(t, name, torch.float32)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"ssd_mix: {name} is {tuple(t.shape)}, expected {shape}")
+    _require(state, "state", torch.float32)
+    if proj.shape[1] != inner + C + heads or out.shape != (n, inner) or tuple(state.shape[1:]) != (heads, state_dim, head_dim):
+        raise KernelError(f"ssd_mix sizes disagree: proj {tuple(proj.shape)}, out {tuple(out.shape)}, state {tuple(state.shape)}")
+    if taps > 1:
+        _require(conv_state, "conv_state", torch.float32)
+        if tuple(conv_state.shape[1:]) != (taps - 1, C):
+            raise KernelError("ssd_mix: the convolution state is [slots, taps - 1, channels]")
+    xbc = torch.empty((n, C), dtype=torch.float32, device=proj.device)
+    y = torch.empty((n, inner), dtype=torch.float32, device=proj.device)
+    args = _SsdArgs(_ptr(proj), _ptr(conv_w), _ptr(conv_b), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(norm_w),
+                    _ptr(conv_state if taps > 1 else None), _ptr(state), _ptr(xbc), _ptr(y), _ptr(out), _ptr(cu_q),
+                    _ptr(tok_seq), _ptr(slots), n, n_seqs, proj.shape[1], heads, head_dim, state_dim, groups, taps,
+                    norm_groups, eps)
+    lib = load_library("ssd")
+    _check(lib.odi_ssd(byref(args), c_int(dtype_code(proj.dtype)), _stream()), "ssd_mix", 4 if taps > 1 else 3)

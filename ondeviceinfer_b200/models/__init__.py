@@ -1,6 +1,7 @@
 """Architectures known to the registry.  Importing this package registers them."""
 
 from ..config.lemesun import LemesunConfig
+from ..config.losivik import LosivikConfig
 from ..config.nulalorn import NulalornConfig
 from ..config.qwen3 import Qwen3Config
 from ..config.zigivik import ZigivikConfig
@@ -8,5 +9,6 @@ from ..registry import register_architecture
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
 register_architecture("Lemesun", LemesunConfig)
+register_architecture("Losivik", LosivikConfig)
 register_architecture("Nulalorn", NulalornConfig)
 register_architecture("Zigivik", ZigivikConfig)

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..cache import StateNeed
-from ..config.specs import ParallelBlockSpec, PreNormBlockSpec, ReinjectSpec, SandwichBlockSpec
+from ..config.specs import ParallelBlockSpec, PreNormBlockSpec, ReinjectSpec, SandwichBlockSpec, ScaledParallelBlockSpec
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
 
@@ -229,6 +229,90 @@ class ParallelBlock(Part):
         ops.scaled_add(hidden, branch, self.spec.residual_mult)
 
 
+class ScaledParallelBlock(Part):
+    """x <- x + s1 * mixer(norm1(x)) + s2 * feed_forward(norm2(x)), then an optional part that adds to the new stream.
+
+    Both norms read the same rows, so ``ops.dual_norm`` makes them in one pass from one sum of squares (the norms
+    must be RMS norms of one eps that scale in fp32).  Each sublayer's fp32 output (a part that says
+    ``returns_output`` returns it; any other adds into a zeroed buffer) is multiplied lane by lane by its stored
+    vector and added in ``ops.scaled_add2``, which also leaves the new rows in the compute dtype for the part after
+    (``after.wants_copy``).  Norms, scales and sums are fp32 in both compute dtypes."""
+
+    def __init__(self, spec: ScaledParallelBlockSpec) -> None:
+        super().__init__(spec)
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        has = spec.ffn is not None
+        if has != (spec.ffn_norm is not None) or has != (spec.ffn_scale_name is not None):
+            raise ValueError("a feed-forward comes with its norm and its scale, or none of the three")
+        self.ffn_norm = build_part(spec.ffn_norm) if has else None
+        self.ffn = build_part(spec.ffn) if has else None
+        self.after = build_part(spec.after) if spec.after is not None else None
+        for norm in (spec.mixer_norm, spec.ffn_norm):
+            if norm is not None and not (getattr(norm, "scale_in_fp32", False) and not getattr(norm, "scalar_weight", False)):
+                raise TypeError("this block's norms are RMS norms with a weight per lane that scale in fp32")
+        self.one_pass = has and spec.mixer_norm.eps == spec.ffn_norm.eps
+
+    def _children(self):
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.after) if part is not None)
+
+    def tensor_decls(self):
+        s = self.spec
+        decls = [d for part in self._children() for d in part.tensor_decls()]
+        decls.append(TensorDecl(s.mixer_scale_name, (s.hidden_size,), "one_plus_normal"))
+        if self.ffn is not None:
+            decls.append(TensorDecl(s.ffn_scale_name, (s.hidden_size,), "one_plus_normal"))
+        return decls
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        for part in self._children():
+            part.load(fetch, runtime)
+        self.mixer_scale = fetch.vector(self.spec.mixer_scale_name)
+        self.ffn_scale = fetch.vector(self.spec.ffn_scale_name) if self.ffn is not None else None
+
+    def cache_needs(self):
+        return tuple(self.mixer.cache_needs())
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self._children())
+
+    def forward(self, hidden, ctx, view) -> None:
+        from ..kernels import ops
+        ctx.defers_residual_add = False        # the parts' own products add (or return) at once
+        ctx.residual_sumsq = None
+        if self.one_pass:
+            h1 = torch.empty(hidden.shape, dtype=self.runtime.dtype, device=hidden.device)
+            h2 = torch.empty_like(h1)
+            ops.dual_norm(hidden, self.mixer_norm.weight, self.ffn_norm.weight, self.mixer_norm.spec.eps, h1, h2)
+        else:
+            h1 = self.mixer_norm(hidden)
+            h2 = self.ffn_norm(hidden) if self.ffn is not None else None
+        if getattr(self.mixer, "returns_output", False):
+            mixed = self.mixer.forward(h1, ctx, view, None)
+        else:
+            mixed = torch.zeros_like(hidden)
+            self.mixer.forward(h1, ctx, view, mixed)
+        fed = None
+        if self.ffn is not None:
+            if getattr(self.ffn, "returns_output", False):
+                fed = self.ffn.forward(h2, ctx, None)
+            else:
+                fed = torch.zeros_like(hidden)
+                self.ffn.forward(h2, ctx, fed)
+        ctx.residual_sumsq = None
+        copy = None
+        if self.after is not None and getattr(self.after, "wants_copy", False):
+            copy = torch.empty(hidden.shape, dtype=self.runtime.dtype, device=hidden.device)
+        ops.scaled_add2(hidden, mixed, self.mixer_scale, fed, self.ffn_scale, copy)
+        if self.after is not None:
+            if copy is not None:
+                self.after.forward(hidden, ctx, copy)
+            else:
+                self.after.forward(hidden, ctx)
+
+
 class Reinject(Part):
     """h <- W [h ; e] + steps[index], e the embedding's output (``ctx.embedded``): what opens a pass of a looped
     stack.  It keeps no cache and returns the new stream (the model goes on with what a layer returns)."""
@@ -261,4 +345,5 @@ class Reinject(Part):
 register_part(PreNormBlockSpec, PreNormBlock)
 register_part(SandwichBlockSpec, SandwichBlock)
 register_part(ParallelBlockSpec, ParallelBlock)
+register_part(ScaledParallelBlockSpec, ScaledParallelBlock)
 register_part(ReinjectSpec, Reinject)

@@ -46,6 +46,10 @@ class CappedAttention(Part):
             raise ValueError("window must be positive")
         if spec.softcap is not None and spec.softcap <= 0:
             raise ValueError("softcap must be positive")
+        if spec.keep_first < 0 or (spec.keep_first > 0 and spec.window is None):
+            raise ValueError("keep_first is a number of first positions kept beside a window")
+        if spec.has("q_norm") != spec.has("k_norm") or (spec.has("q_norm") and spec.unit_norm_eps is None):
+            raise ValueError("weights of the per-head norm come in a pair and go with unit_norm_eps")
         self.position = build_part(spec.position)
         if self.position.rot_dim > 0 and not getattr(self.position, "interleaved", False):
             raise ValueError("this attention's head preparation rotates neighbouring-lane pairs only")
@@ -60,6 +64,7 @@ class CappedAttention(Part):
             decls.append(TensorDecl(s.name("v"), (v, s.hidden_size)))
         decls.append(TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.value_dim)))
         decls += [TensorDecl(s.name(role), (size,)) for role, size in (("q_bias", q), ("k_bias", k)) if s.has(role)]
+        decls += [TensorDecl(s.name(role), (s.head_dim,), "one_plus_normal") for role in ("q_norm", "k_norm") if s.has(role)]
         return decls + self.position.tensor_decls()
 
     def load(self, fetch, runtime) -> None:
@@ -80,11 +85,13 @@ class CappedAttention(Part):
             self.b_qkv = torch.cat([fetch.vector(s.name(role)) if s.has(role)
                                     else torch.zeros(size, dtype=torch.float32, device=runtime.device)
                                     for role, size in sizes])
+        self.q_norm_w = fetch.vector(s.name("q_norm")) if s.has("q_norm") else None
+        self.k_norm_w = fetch.vector(s.name("k_norm")) if s.has("k_norm") else None
         self.position.load(fetch, runtime)
 
     def cache_needs(self):
         s = self.spec
-        return (KVNeed(s.num_kv_heads, self.lanes, s.window, value_dim=s.value_dim),)
+        return (KVNeed(s.num_kv_heads, self.lanes, s.window, value_dim=s.value_dim, keep_first=s.keep_first),)
 
     # ------------------------------------------------------------------ step
 
@@ -101,7 +108,7 @@ class CappedAttention(Part):
                           ctx.tok_pos, page_start, page_ids, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim,
                           dv=s.value_dim, rot_dim=self.position.rot_dim, page_size=PAGE_SIZE, ring_pages=group.ring_pages,
                           write_kv=view.writes_kv, unit_eps=s.unit_norm_eps, d_store=self.lanes,
-                          v_from_k=s.values_are_keys)
+                          v_from_k=s.values_are_keys, q_weight=self.q_norm_w, k_weight=self.k_norm_w)
         o = self.attend(q, ctx, view, page_start, page_ids)
         if residual is None:
             return linear(o, self.w_o, out_dtype=torch.float32)
@@ -115,9 +122,9 @@ class CappedAttention(Part):
         tensor_cores = ops.attention_capped_supported(q.dtype, self.lanes, s.value_dim)
         common = dict(n_seqs=ctx.n_seqs, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, dv=s.value_dim, page_size=PAGE_SIZE,
                       ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0,
-                      sink=s.sink)
+                      sink=s.sink, keep=s.keep_first)
         if (tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and self.lanes == s.value_dim
-                and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS):
+                and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS and s.keep_first == 0):
             # bf16 prompts with heads of 64 or 128 lanes: scores and outputs in tensor memory (tcgen05)
             ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
                                   max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, page_size=PAGE_SIZE,
@@ -133,9 +140,10 @@ class CappedAttention(Part):
         if ctx.max_q_len == 1:
             # single tokens: cut the visible keys so that enough blocks run side by side
             block_rows = s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
-            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window)
+            keys = ctx.max_kv_len if s.window is None else min(ctx.max_kv_len, s.window + s.keep_first)
             if tensor_cores:
                 tiles = (keys + 63) // 64 + (1 if s.window is not None else 0)      # a window may straddle one tile more
+                tiles += 1 if s.keep_first > 0 else 0                               # and so may the kept first keys
                 splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), tiles))
             else:
                 splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), (keys + 255) // 256))

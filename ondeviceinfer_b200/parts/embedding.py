@@ -23,7 +23,10 @@ from .linear import linear
 
 class TokenEmbedding(Part):
     """hidden[t, :] = table[token[t], :], widened into the fp32 residual stream; with a norm in the spec the rows
-    then pass it, in fp32 (a norm that scales in fp32)."""
+    then pass it, in fp32 (a norm that scales in fp32).  With ``sinusoid_base`` in the spec the rows are multiplied
+    by ``scale`` and get an absolute sinusoidal position vector in the same kernel: the frequencies
+    base^(-2i / hidden) are computed here in double and rounded once, the angle position * frequency and its sine
+    and cosine are fp32 on the device."""
 
     graph_safe = True
 
@@ -40,10 +43,22 @@ class TokenEmbedding(Part):
         self.table = fetch.matrix(self.spec.weight_name)
         if self.norm is not None:
             self.norm.load(fetch, runtime)
+        self.scale = float(getattr(self.spec, "scale", 1.0))
+        base = getattr(self.spec, "sinusoid_base", None)
+        self.inv_freq = None
+        if base is not None:
+            H = self.spec.hidden_size
+            self.inv_freq = torch.tensor([float(base) ** (-2.0 * i / H) for i in range((H + 1) // 2)],
+                                         dtype=torch.float64).to(torch.float32).to(runtime.device)
+        elif self.scale != 1.0:
+            raise ValueError("a scaled embedding without positions is not implemented")
 
     def forward(self, ctx) -> torch.Tensor:
         hidden = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.embed(self.table, ctx.token_ids, hidden)
+        if self.inv_freq is not None:
+            ops.embed_sinusoid(self.table, ctx.token_ids, ctx.tok_pos, self.inv_freq, hidden, self.scale)
+        else:
+            ops.embed(self.table, ctx.token_ids, hidden)
         if self.norm is not None:
             return self.norm(hidden, out_dtype=torch.float32)
         return hidden

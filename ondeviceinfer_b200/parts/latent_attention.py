@@ -87,7 +87,7 @@ class LatentAttention(Part):
         decls += [TensorDecl(s.name("uk"), (s.num_heads * s.qk_dim, s.kv_rank)),
                   TensorDecl(s.name("uv"), (s.num_heads * s.v_dim, s.kv_rank))]
         if s.gated:
-            decls.append(TensorDecl(s.name("g"), (s.num_heads * s.v_dim, s.hidden_size)))
+            decls.append(TensorDecl(s.name("g"), (s.num_heads * (1 if s.gate_per_head else s.v_dim), s.hidden_size)))
         return decls + [TensorDecl(s.name("o"), (s.hidden_size, s.num_heads * s.v_dim))] + self.position.tensor_decls()
 
     def load(self, fetch, runtime) -> None:
@@ -98,10 +98,18 @@ class LatentAttention(Part):
         # [down projection | query latent | gate], the down projection first so that its lanes start a row.
         self.w_gate = self.w_uq = self.q_norm = None
         down = [fetch.matrix(s.name("dkv"))] if s.own_kv else []
+        self.gate_in_first = False
         if s.q_rank is None:
-            self.w_in = torch.cat([fetch.matrix(s.name("q"))] + down, 0)
-            if s.gated:
+            rows = [fetch.matrix(s.name("q"))] + down
+            if s.gated and s.gate_per_head:
+                # a gate of one row per head is too small for a product of its own: its rows follow the others,
+                # with zero rows up to a multiple of eight so that the product's rows stay 16-byte aligned
+                g = fetch.matrix(s.name("g"))
+                rows += [g, torch.zeros(((-s.num_heads) % 8, s.hidden_size), dtype=g.dtype, device=g.device)]
+                self.gate_in_first = True
+            elif s.gated:
                 self.w_gate = fetch.matrix(s.name("g"))
+            self.w_in = torch.cat(rows, 0)
         else:
             self.w_in = torch.cat(down + [fetch.matrix(s.name("dq"))] + ([fetch.matrix(s.name("g"))] if s.gated else []), 0)
             self.w_uq = fetch.matrix(s.name("uq"))
@@ -133,7 +141,9 @@ class LatentAttention(Part):
         gate, gate_col, down = None, 0, None
         if s.q_rank is None:
             queries = proj          # with the down projection behind the heads, if the layer has one
-            if s.gated:
+            if self.gate_in_first:
+                gate, gate_col = proj, s.num_heads * (s.qk_dim + s.rot_dim) + (s.kv_rank + s.rot_dim if s.own_kv else 0)
+            elif s.gated:
                 gate = linear(x, self.w_gate)
         else:
             at = s.kv_rank + s.rot_dim if s.own_kv else 0
@@ -160,7 +170,8 @@ class LatentAttention(Part):
                         rot_dims=self.position.rot_dim if cos is not None else 0,
                         interleaved=getattr(self.position, "interleaved", False), page_size=PAGE_SIZE,
                         ring_pages=group.ring_pages, write_cache=s.own_kv and view.writes_kv, eps=s.norm_eps,
-                        latent_out=latent, key_rot_out=key_rot, row=self.row, down=down, has_down=s.own_kv)
+                        latent_out=latent, key_rot_out=key_rot, row=self.row, down=down, has_down=s.own_kv,
+                        trailing=-(-s.num_heads // 8) * 8 if self.gate_in_first else 0)
         if step_whole:
             if s.own_kv and view.writes_kv:
                 ctx.memo(shared_key, lambda: (latent, key_rot))
@@ -178,7 +189,7 @@ class LatentAttention(Part):
                                    c_stride=s.v_dim, K=s.kv_rank)
             w_o, lanes = self.w_o, s.v_dim
         if s.gated:
-            ops.gate_heads(out, gate, heads=s.num_heads, dv=s.v_dim, lanes=lanes, col=gate_col)
+            ops.gate_heads(out, gate, heads=s.num_heads, dv=s.v_dim, lanes=lanes, col=gate_col, per_head=s.gate_per_head)
         if residual is None:
             return linear(out, w_o, out_dtype=torch.float32)
         linear(out, w_o, residual=residual, track=ctx)

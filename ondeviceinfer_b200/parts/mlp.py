@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedMLPSpec, MLPSpec, PolyNormMLPSpec
+from ..config.specs import ClampedGatedMLPSpec, GatedMLPSpec, MLPSpec, PolyNormMLPSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
@@ -104,6 +104,51 @@ class PolyNormMLP(Part):
         return None
 
 
+class ClampedGatedMLP(Part):
+    """down(g * sigmoid(alpha g) * (u + 1)) with g = min(gate x, limit), u = clamp(up x, -limit, limit), biases on the
+    projections that the spec names one for.  Gate and up rows are concatenated at load: one product (the biases join
+    its fp32 sums), then ``ops.gated_clamp`` (fp32 arithmetic, one rounding), then the down product."""
+
+    graph_safe = True
+    returns_output = True   # forward(..., residual=None) returns the fp32 output instead of adding it
+
+    def __init__(self, spec: ClampedGatedMLPSpec) -> None:
+        super().__init__(spec)
+        if spec.limit <= 0:
+            raise ValueError("limit must be positive")
+
+    def tensor_decls(self):
+        s = self.spec
+        decls = [TensorDecl(s.name("gate"), (s.intermediate_size, s.hidden_size)),
+                 TensorDecl(s.name("up"), (s.intermediate_size, s.hidden_size)),
+                 TensorDecl(s.name("down"), (s.hidden_size, s.intermediate_size))]
+        sizes = (("gate_bias", s.intermediate_size), ("up_bias", s.intermediate_size), ("down_bias", s.hidden_size))
+        return decls + [TensorDecl(s.name(role), (size,)) for role, size in sizes if s.has(role)]
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        self.w_gate_up = torch.cat([fetch.matrix(s.name("gate")), fetch.matrix(s.name("up"))], 0)
+        self.w_down = fetch.matrix(s.name("down"))
+        self.b_gate_up = None
+        if s.has("gate_bias") or s.has("up_bias"):       # a projection without a bias adds zero
+            self.b_gate_up = torch.cat([fetch.vector(s.name(role)) if s.has(role)
+                                        else torch.zeros(s.intermediate_size, dtype=torch.float32, device=runtime.device)
+                                        for role in ("gate_bias", "up_bias")])
+        self.b_down = fetch.vector(s.name("down_bias")) if s.has("down_bias") else None
+
+    def forward(self, x, ctx, residual):
+        """Adds to ``residual`` (fp32); with ``residual`` None returns the output as a new fp32 tensor."""
+        s = self.spec
+        act = torch.empty((x.shape[0], s.intermediate_size), dtype=x.dtype, device=x.device)
+        ops.gated_clamp(linear(x, self.w_gate_up, bias=self.b_gate_up), act, s.limit, s.alpha)
+        if residual is None:
+            return linear(act, self.w_down, bias=self.b_down, out_dtype=torch.float32)
+        linear(act, self.w_down, bias=self.b_down, residual=residual)
+        return None
+
+
+register_part(ClampedGatedMLPSpec, ClampedGatedMLP)
 register_part(GatedMLPSpec, GatedMLP)
 register_part(PolyNormMLPSpec, PolyNormMLP)
 register_part(MLPSpec, PlainMLP)
