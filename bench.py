@@ -34,7 +34,7 @@ lengths and with temperature sampling.  One JSON line is printed:
 on the same configuration, and prints the same line with ``"impl": "reference"``.  Nothing of
 this library is imported in that arm.
 
-``--design lemesun`` (or ``nulalorn``, ``zigivik``) leaves the default workload alone and measures that architecture instead: prefill and
+``--design lemesun`` (or ``nulalorn``, ``zigivik``, ``losivik``) leaves the default workload alone and measures that architecture instead: prefill and
 decode throughput at layer sizes like a real model's beside the dense model of equal width, one JSON line
 (``run_design_points``).
 
@@ -630,6 +630,29 @@ def _zigivik_config(width, heads, kv_heads, dim, latent_dim, rot, vdim, rank, q_
             "canon": {"taps": 4}, "layers": [attention, latent, attention, reader]}
 
 
+def _losivik_config(width, heads, kv_heads, dim, rank, window, keep, ssm_heads, ssm_dim, state, experts, top, ff, shared_ff,
+                    dense_ff, side, vocab):
+    """Four layers: latent attention with a dense feed-forward, attention beside a state-space mixer with routed
+    experts, and both once more."""
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": dense_ff, "limit": 7.0},
+              "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": dim ** -0.5, "mask": {"size": window}}}
+    pair = {"type": "parallel",
+            "mlp": {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared_ff}, "router": {"experts": experts, "top": top}},
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                               "mask": {"size": window, "keep_first": keep}},
+                      "right": {"heads": ssm_heads, "vdim": ssm_dim, "state": state, "groups": 1, "conv": 4, "norm_groups": 1},
+                      "left_scale": 0.5, "right_scale": 0.5}}
+    return {"architecture": "Losivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "token_side": {"dim": side}, "layers": [latent, pair, latent, pair]}
+
+
+LOSIVIK_POINTS = {
+    "w2048": (_losivik_config(2048, 16, 4, 128, 512, 1024, 64, 32, 64, 128, 32, 4, 1024, 1024, 5 * 1024, 256, 32768),
+              _dense_config(2048, 16, 5 * 1024, 4, 32768)),
+    "w4096": (_losivik_config(4096, 32, 8, 128, 512, 1024, 64, 64, 64, 128, 64, 6, 1536, 3072, 12288, 256, 32768),
+              _dense_config(4096, 32, 12288, 4, 32768)),
+}
+
 ZIGIVIK_POINTS = {
     "w2048": (_zigivik_config(2048, 16, 4, 128, 64, 64, 128, 512, 768, 1024, 5 * 1024, 32768),
               _dense_config(2048, 16, 5 * 1024, 4, 32768)),
@@ -657,7 +680,10 @@ def _time_parts(model, cache, slots, runs, torch):
     """Device time of every mixer and feed-forward call of one step, by part class: {name: [us, calls]}."""
     events, restore = [], []
     for block in model.decoder.layers:
-        for part in (getattr(block, "mixer", None), getattr(block, "ffn", None)):
+        mixer = getattr(block, "mixer", None)
+        # two mixers side by side are timed each for itself as well; so is a part that runs after the layer's add
+        for part in (mixer, getattr(block, "ffn", None), getattr(mixer, "left", None), getattr(mixer, "right", None),
+                     getattr(block, "after", None)):
             if part is None:
                 continue
             original = part.forward
@@ -686,7 +712,7 @@ def _time_parts(model, cache, slots, runs, torch):
 
 
 def run_design_points(args) -> int:
-    """``--design lemesun|nulalorn|zigivik``: prefill and decode throughput of that design at layer sizes like a real model's
+    """``--design lemesun|nulalorn|zigivik|losivik``: prefill and decode throughput of that design at layer sizes like a real model's
     (random weights), each beside the dense Qwen3 model of equal width, heads, layer executions and active
     feed-forward width, with the device time of every mixer and feed-forward call.  One JSON line; the default
     workload is untouched."""
@@ -704,7 +730,7 @@ def run_design_points(args) -> int:
     points = {}
     sampler = ClockSampler()
     sampler.start()
-    design_points = {"nulalorn": NULALORN_POINTS, "zigivik": ZIGIVIK_POINTS}.get(args.design, DESIGN_POINTS)
+    design_points = {"nulalorn": NULALORN_POINTS, "zigivik": ZIGIVIK_POINTS, "losivik": LOSIVIK_POINTS}.get(args.design, DESIGN_POINTS)
     for name, configs in design_points.items():
         if args.design_points and name not in args.design_points.split(","):
             continue
@@ -789,7 +815,7 @@ def main() -> int:
     parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
                         help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
     parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
-    parser.add_argument("--design", default=None, choices=["lemesun", "nulalorn", "zigivik"],
+    parser.add_argument("--design", default=None, choices=["lemesun", "nulalorn", "zigivik", "losivik"],
                         help="instead of the default workload: this design at real layer sizes beside the dense model of equal size")
     parser.add_argument("--design-points", default=None, help="which of the design's sizes, with commas (default: all)")
     args = parser.parse_args()

@@ -90,6 +90,7 @@ struct TcAttnArgs {
   int ring_pages;         // > 0: a sequence's page list is a ring: the page of position p is entry (p / 64) % ring_pages
   float softcap;          // c > 0: a score (times scale) becomes c tanh(score / c) before the softmax
   int sink;               // 1: the softmax has one more term, of score 0 and without a value
+  int keep;               // > 0 with a window: keys 0..keep-1 stay visible beyond the window; their tiles come first in the walk
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -265,7 +266,8 @@ __device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, ui
 struct RowState { float m_used, l; };
 __device__ __forceinline__ bool softmax_keys64(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int kbase, int pos, float sl2,
                                                int n, uint32_t pv_done, RowState& st, volatile int* abort_ptr,
-                                               int oldest = 0, float scale = 1.f, float cap = 0.f, float two_over_cap = 0.f) {
+                                               int oldest = 0, float scale = 1.f, float cap = 0.f, float two_over_cap = 0.f,
+                                               int keep = 0) {
   float s[BNK];
   tmem_ld64(s_addr, s);
   if (cap > 0.f) {
@@ -278,7 +280,10 @@ __device__ __forceinline__ bool softmax_keys64(uint32_t s_addr, uint32_t p_addr,
     for (int i = 0; i < BNK; ++i) mx = fmaxf(mx, s[i]);
   } else {
 #pragma unroll
-    for (int i = 0; i < BNK; ++i) { if (kbase + i > pos || kbase + i < oldest) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
+    for (int i = 0; i < BNK; ++i) {
+      if (kbase + i > pos || (kbase + i < oldest && kbase + i >= keep)) s[i] = -INFINITY;
+      mx = fmaxf(mx, s[i]);
+    }
   }
   // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
   // what O holds for the row was taken against the old one and is scaled down first.  The
@@ -368,7 +373,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int nt = min(BM, q_len - t0);
   // key tiles from the one that holds the oldest key any row of the CTA sees up to the diagonal
   const int tile_lo = a.window > 0 ? max(0, past + t0 - a.window + 1) / BNK : 0;
-  const int n_tiles = (past + t0 + nt + BNK - 1) / BNK - tile_lo;
+  // in front of them the tiles of kept first keys that lie before the window's first tile
+  const int keep_tiles = a.window > 0 && a.keep > 0 ? min((a.keep + BNK - 1) / BNK, tile_lo) : 0;
+  const int n_tiles = keep_tiles + (past + t0 + nt + BNK - 1) / BNK - tile_lo;
+  auto tile_of = [&](int j) { return j < keep_tiles ? j : tile_lo + (j - keep_tiles); };
   const int* pages = a.page_ids + a.page_start[seq];
 
   const uint32_t bar0 = smem_u32(&bars[0]);
@@ -408,7 +416,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       auto load_page = [&](int j, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
         const int s = j % RING;
         if (!mbar_wait(empty + 8 * s, ((uint32_t)(j / RING) & 1u) ^ 1u, abort_ptr)) { ok = false; return; }
-        const int entry = page_slot_of_page(tile_lo + j, a.ring_pages);
+        const int entry = page_slot_of_page(tile_of(j), a.ring_pages);
         const int row = (pages[entry] * a.nkv + hk) * BNK;
         mbar_expect_tx(full + 8 * s, KV_BYTES);
         for (int kb = 0; kb < KB; ++kb)
@@ -493,8 +501,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + S_COL(tile, b);
       // P_j goes over the first 32 columns of this row's scores
-      if (!softmax_keys64(s_addr, s_addr, o_addr, (tile_lo + j) * BNK, pos, sl2, j, my_pv_done, st, abort_ptr, oldest, a.scale,
-                          a.softcap, two_over_cap)) { ok = false; break; }
+      if (!softmax_keys64(s_addr, s_addr, o_addr, tile_of(j) * BNK, pos, sl2, j, my_pv_done, st, abort_ptr, oldest, a.scale,
+                          a.softcap, two_over_cap, a.keep)) { ok = false; break; }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_p_full + 8 * b);

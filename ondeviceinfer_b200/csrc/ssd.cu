@@ -11,17 +11,18 @@
 //  scan        per sequence and head h (group g = h / (heads / G)), over the sequence's tokens in order:
 //                dt = softplus(dt_raw + dt_bias[h]);  S <- exp(-exp(A_log[h]) dt) S + dt B_g x_h^T;  y = S^T C_g + D[h] x_h
 //              with S [N, P] fp32 per (sequence, head), kept in the cache between steps.  A block owns 32 columns of S;
-//              a column lives in the registers of 8 lanes (every 8th row each), the read-out is a sum over those
-//              lanes; 16 tokens of B, C, x and the decays are staged in shared memory at a time.
+//              a column lives in the registers of 8 lanes, the read-out is a sum over those lanes; 16 tokens of B, C, x
+//              and the decays are staged in shared memory at a time, the next 16 by asynchronous copies meanwhile.
 //  gate_norm   v = y * silu(z); v is RMS-normed in `norm_groups` equal parts of a token's row (each part by its own
 //              root mean square, eps inside the root), times a weight per lane, rounded once to T.
 //
 // Everything but the projection's own output is fp32 in both compute dtypes.
 #include "common.cuh"
+#include <type_traits>
 
 #define SSD_MAX_TAPS 16
 #define SSD_TCH 16          // tokens staged at a time
-#define SSD_COLS 32         // columns of S per block
+#define SSD_COLS 32         // most columns of S per block (a kernel form takes 32 or 8)
 #define SSD_LANES 8         // lanes that share a column
 
 struct SsdArgs {
@@ -92,77 +93,149 @@ ssd_conv_state_kernel(SsdArgs a) {
     if (j < keep) a.conv_state[((size_t)slot * keep + j) * C + c] = next[j];
 }
 
-// NPT: rows of S per lane (N <= 8 NPT).
-template <typename T, int NPT>
-__global__ void __launch_bounds__(SSD_COLS * SSD_LANES)
+__device__ __forceinline__ void ssd_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ssd_cp16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ssd_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ssd_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// NPT: rows of S per lane (N <= 8 NPT).  VEC (N a multiple of 4, 16-byte aligned rows of xbc): a lane owns rows
+// 4 (ns + 8 j) .. + 3 of its column and reads B and C four at a time; else rows ns + 8 k, one at a time.
+// Two staging buffers: while the block works through one chunk of SSD_TCH tokens, the asynchronous copies of the next
+// chunk's B, C and x (and the loads of its step sizes) are in flight; one barrier per chunk.
+// COLS: columns of S per block (COLS * 8 threads): fewer columns make more blocks, which is what a step of one long
+// sequence needs, since each warp's time is the chain of its tokens.
+template <typename T, int NPT, bool VEC, int COLS>
+__global__ void __launch_bounds__(COLS * SSD_LANES)
 ssd_scan_kernel(SsdArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float ssd_smem[];
+  extern __shared__ __align__(16) float ssd_smem[];
   const int N = a.N, P = a.P, inner = a.heads * P, C = inner + 2 * a.G * N;
-  float* sB = ssd_smem;                       // [TCH][N]
-  float* sC = sB + SSD_TCH * N;               // [TCH][N]
-  float* sX = sC + SSD_TCH * N;               // [TCH][COLS]
-  float* sDt = sX + SSD_TCH * SSD_COLS;       // [TCH]
-  float* sDa = sDt + SSD_TCH;                 // [TCH]
+  const int stage = SSD_TCH * (2 * N + COLS) + 2 * SSD_TCH;      // floats of one buffer
   const int tid = threadIdx.x, ns = tid % SSD_LANES, pc = tid / SSD_LANES;
   const int h = blockIdx.y, seq = blockIdx.z, g = h / (a.heads / a.G);
-  const int p0 = blockIdx.x * SSD_COLS, p = p0 + pc;
+  const int p0 = blockIdx.x * COLS, p = p0 + pc;
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
   if (q_len <= 0) return;
   const int slot = a.slots[seq];
   float* S = a.state + ((size_t)slot * a.heads + h) * N * P;
+  auto row_of = [&](int k) { return VEC ? 4 * (ns + SSD_LANES * (k >> 2)) + (k & 3) : ns + SSD_LANES * k; };
   float s[NPT];
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
-    const int n = ns + SSD_LANES * k;
+    const int n = row_of(k);
     s[k] = (n < N && p < P) ? S[(size_t)n * P + p] : 0.f;
   }
   const float neg_a = -expf(a.a_log[h]), dt_b = a.dt_bias[h], dskip = a.d_skip[h];
-  const T* proj = (const T*)a.proj;
-  for (int base = 0; base < q_len; base += SSD_TCH) {
-    const int nt = min(SSD_TCH, q_len - base);
-    __syncthreads();      // the chunk before has been consumed
-    for (int i = tid; i < nt * N; i += blockDim.x) {
-      const int tt = i / N, n = i % N;
-      const float* row = a.xbc + (size_t)(q_begin + base + tt) * C + inner + (size_t)g * N;
-      sB[tt * N + n] = row[n];
-      sC[tt * N + n] = row[(size_t)a.G * N + n];
+  const T* dt_col = (const T*)a.proj + 2 * inner + 2 * a.G * N + h;
+  const int n_chunks = (q_len + SSD_TCH - 1) / SSD_TCH;
+
+  // buffer layout: B [TCH][N], C [TCH][N], x [TCH][COLS], dt [TCH], decay [TCH]
+  auto issue = [&](int c) {
+    float* buf = ssd_smem + (size_t)(c & 1) * stage;
+    const int base = c * SSD_TCH, nt = min(SSD_TCH, q_len - base);
+    const float* rows = a.xbc + (size_t)(q_begin + base) * C;
+    if (VEC) {
+      const int n4 = N / 4;
+      for (int i = tid; i < nt * n4; i += blockDim.x) {
+        const int tt = i / n4, j = (i % n4) * 4;
+        const float* src = rows + (size_t)tt * C + inner + (size_t)g * N + j;
+        ssd_cp16(buf + tt * N + j, src);
+        ssd_cp16(buf + SSD_TCH * N + tt * N + j, src + (size_t)a.G * N);
+      }
+    } else {
+      for (int i = tid; i < nt * N; i += blockDim.x) {
+        const int tt = i / N, n = i % N;
+        const float* src = rows + (size_t)tt * C + inner + (size_t)g * N + n;
+        ssd_cp4(buf + tt * N + n, src);
+        ssd_cp4(buf + SSD_TCH * N + tt * N + n, src + (size_t)a.G * N);
+      }
     }
-    for (int i = tid; i < nt * SSD_COLS; i += blockDim.x) {
-      const int tt = i / SSD_COLS, cc = i % SSD_COLS;
-      sX[i] = p0 + cc < P ? a.xbc[(size_t)(q_begin + base + tt) * C + (size_t)h * P + p0 + cc] : 0.f;
+    float* sX = buf + 2 * SSD_TCH * N;
+    for (int i = tid; i < nt * COLS; i += blockDim.x) {
+      const int tt = i / COLS, cc = i % COLS;
+      if (p0 + cc < P) ssd_cp4(sX + i, rows + (size_t)tt * C + (size_t)h * P + p0 + cc);
+      else sX[i] = 0.f;
     }
-    if (tid < nt) {
-      const float raw = to_f<T>(proj[(size_t)(q_begin + base + tid) * a.ld + 2 * inner + 2 * a.G * N + h]);
-      const float dt = ssd_softplus(raw + dt_b);
-      sDt[tid] = dt;
-      sDa[tid] = expf(neg_a * dt);
+    ssd_cp_commit();
+  };
+  auto step_sizes = [&](int c, float raw) {      // by thread tid < tokens of chunk c
+    float* buf = ssd_smem + (size_t)(c & 1) * stage + SSD_TCH * (2 * N + COLS);
+    const float dt = ssd_softplus(raw + dt_b);
+    buf[tid] = dt;
+    buf[SSD_TCH + tid] = expf(neg_a * dt);
+  };
+
+  issue(0);
+  if (tid < min(SSD_TCH, q_len)) step_sizes(0, to_f<T>(dt_col[(size_t)(q_begin + tid) * a.ld]));
+  for (int c = 0; c < n_chunks; ++c) {
+    ssd_cp_wait_all();
+    __syncthreads();      // chunk c is in its buffer; everybody has left chunk c - 1, whose buffer takes chunk c + 1
+    const int base = c * SSD_TCH, nt = min(SSD_TCH, q_len - base);
+    const bool more = c + 1 < n_chunks;
+    const int nt_next = more ? min(SSD_TCH, q_len - base - SSD_TCH) : 0;
+    float raw_next = 0.f;
+    if (more) {
+      issue(c + 1);
+      if (tid < nt_next) raw_next = to_f<T>(dt_col[(size_t)(q_begin + base + SSD_TCH + tid) * a.ld]);
     }
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float x = sX[tt * SSD_COLS + pc], dt = sDt[tt], da = sDa[tt];
+    const float* buf = ssd_smem + (size_t)(c & 1) * stage;
+    const float* sB = buf;
+    const float* sC = buf + SSD_TCH * N;
+    const float* sX = buf + 2 * SSD_TCH * N;
+    const float* sDt = sX + SSD_TCH * COLS;
+    const float* sDa = sDt + SSD_TCH;
+    // one token: the state's rows of this lane move on, the read-out is summed over the column's lanes
+    auto token = [&](int tt, auto full_tag) {
+      constexpr bool FULL = decltype(full_tag)::value;      // N == 8 NPT: no row of the lane lies beyond the state
+      const float x = sX[tt * COLS + pc], dt = sDt[tt], da = sDa[tt];
       const float dx = dt * x;
       const float* B = sB + tt * N;
       const float* Cc = sC + tt * N;
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (VEC) {
 #pragma unroll
-      for (int k = 0; k < NPT; ++k) {
-        const int n = ns + SSD_LANES * k;
-        if (n < N) {
-          s[k] = fmaf(da, s[k], dx * B[n]);
-          acc = fmaf(s[k], Cc[n], acc);
+        for (int j = 0; j < NPT / 4; ++j) {
+          const int n = 4 * (ns + SSD_LANES * j);
+          if (FULL || n < N) {
+            const float4 b = *(const float4*)(B + n), cv = *(const float4*)(Cc + n);
+            s[4 * j] = fmaf(da, s[4 * j], dx * b.x);         acc[0] = fmaf(s[4 * j], cv.x, acc[0]);
+            s[4 * j + 1] = fmaf(da, s[4 * j + 1], dx * b.y); acc[1] = fmaf(s[4 * j + 1], cv.y, acc[1]);
+            s[4 * j + 2] = fmaf(da, s[4 * j + 2], dx * b.z); acc[2] = fmaf(s[4 * j + 2], cv.z, acc[2]);
+            s[4 * j + 3] = fmaf(da, s[4 * j + 3], dx * b.w); acc[3] = fmaf(s[4 * j + 3], cv.w, acc[3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < NPT; ++k) {
+          const int n = ns + SSD_LANES * k;
+          if (FULL || n < N) {
+            s[k] = fmaf(da, s[k], dx * B[n]);
+            acc[k & 3] = fmaf(s[k], Cc[n], acc[k & 3]);
+          }
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (ns == 0 && p < P) a.y[(size_t)(q_begin + base + tt) * inner + (size_t)h * P + p] = fmaf(dskip, x, acc);
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (ns == 0 && p < P) a.y[(size_t)(q_begin + base + tt) * inner + (size_t)h * P + p] = fmaf(dskip, x, sum);
+    };
+    if (N == SSD_LANES * NPT) {
+#pragma unroll 2
+      for (int tt = 0; tt < nt; ++tt) token(tt, std::true_type{});
+    } else {
+      for (int tt = 0; tt < nt; ++tt) token(tt, std::false_type{});
     }
+    if (more && tid < nt_next) step_sizes(c + 1, raw_next);
   }
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
-    const int n = ns + SSD_LANES * k;
+    const int n = row_of(k);
     if (n < N && p < P) S[(size_t)n * P + p] = s[k];
   }
 }
@@ -198,12 +271,25 @@ static int ssd_launch(const SsdArgs& a, cudaStream_t stream) {
   odi_rc = launch_pdl((ssd_conv_kernel<T>), dim3(a.n_tokens, (C + 255) / 256), dim3(256), 0, stream, a);
   if (odi_rc == 0 && a.taps > 1)
     odi_rc = launch_pdl((ssd_conv_state_kernel<T>), dim3(a.n_seqs, (C + 255) / 256), dim3(256), 0, stream, a);
-  const dim3 grid((a.P + SSD_COLS - 1) / SSD_COLS, a.heads, a.n_seqs);
-  const size_t smem = sizeof(float) * (SSD_TCH * (2 * (size_t)a.N + SSD_COLS) + 2 * SSD_TCH);
+  // 32 columns a block when that already gives two blocks per multiprocessor, else 8
+  const bool narrow = (long)((a.P + 31) / 32) * a.heads * a.n_seqs < 2 * 148;
+  const int cols = narrow ? 8 : SSD_COLS;
+  const dim3 grid((a.P + cols - 1) / cols, a.heads, a.n_seqs);
+  const size_t smem = 2 * sizeof(float) * (SSD_TCH * (2 * (size_t)a.N + cols) + 2 * SSD_TCH);
+  const int C_all = a.heads * a.P + 2 * a.G * a.N;
+  const bool vec = a.N % 4 == 0 && C_all % 4 == 0 && (a.heads * a.P) % 4 == 0 && ((uintptr_t)a.xbc & 15) == 0;
   if (odi_rc == 0) {
-#define ODI_SCAN(NPT) odi_rc = launch_pdl((ssd_scan_kernel<T, NPT>), grid, dim3(SSD_COLS * SSD_LANES), smem, stream, a)
+#define ODI_SCAN_FORM(NPT, VEC, COLS) \
+    do { if (smem > 48 * 1024) { \
+           const cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, VEC, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+           if (e != cudaSuccess) return (int)e; } \
+         odi_rc = launch_pdl((ssd_scan_kernel<T, NPT, VEC, COLS>), grid, dim3(COLS * SSD_LANES), smem, stream, a); } while (0)
+#define ODI_SCAN(NPT) \
+    do { if (vec) { if (narrow) ODI_SCAN_FORM(NPT, true, 8); else ODI_SCAN_FORM(NPT, true, 32); } \
+         else { if (narrow) ODI_SCAN_FORM(NPT, false, 8); else ODI_SCAN_FORM(NPT, false, 32); } } while (0)
     if (a.N <= 32) ODI_SCAN(4); else if (a.N <= 64) ODI_SCAN(8); else if (a.N <= 128) ODI_SCAN(16); else ODI_SCAN(32);
 #undef ODI_SCAN
+#undef ODI_SCAN_FORM
   }
   if (odi_rc == 0)
     odi_rc = launch_pdl((ssd_gate_norm_kernel<T>), dim3(a.n_tokens, a.norm_groups), dim3(256), 0, stream, a);

@@ -876,7 +876,8 @@ def attention_mma_combine(partial: torch.Tensor, out: torch.Tensor, past: torch.
 class _TcAttnArgs(Structure):
     _fields_ = [("out", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("status", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int),
-                ("scale", c_float), ("window", c_int), ("ring_pages", c_int), ("softcap", c_float), ("sink", c_int)]
+                ("scale", c_float), ("window", c_int), ("ring_pages", c_int), ("softcap", c_float), ("sink", c_int),
+                ("keep", c_int)]
 
 
 TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
@@ -884,7 +885,7 @@ TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
 
 def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, heads_per_cta: int = 0, window: int = 0,
-                      ring_pages: int = 0, softcap: float = 0.0, sink: bool = False) -> None:
+                      ring_pages: int = 0, softcap: float = 0.0, sink: bool = False, keep: int = 0) -> None:
     """bf16 causal GQA for prefill on tcgen05: scores and outputs in tensor memory, TMA-fed pages.
     ``sink``: one more term of score 0 and no value in the softmax.
     ``window`` > 0 keeps the last ``window`` keys visible (``ring_pages`` > 0: the page lists are rings);
@@ -902,7 +903,7 @@ def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, 
         raise KernelError("attention_tcgen05: q/out or the pools disagree")
     _, _, status = _gemm_buffers(q.device, 0)
     args = _TcAttnArgs(_ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start), _ptr(page_ids), _ptr(status),
-                       n_seqs, nq, nkv, scale, window, ring_pages, softcap, 1 if sink else 0)
+                       n_seqs, nq, nkv, scale, window, ring_pages, softcap, 1 if sink else 0, keep)
     lib = load_library("attention_tcgen05", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), byref(args), c_int(n_tokens),
                                      c_int(max_q_len), c_long(k_pool.shape[0]), c_int(heads_per_cta), _stream()),

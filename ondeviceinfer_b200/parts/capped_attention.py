@@ -124,12 +124,12 @@ class CappedAttention(Part):
                       ring_pages=view.kv_group.ring_pages, window=s.window or 0, scale=s.scale, softcap=s.softcap or 0.0,
                       sink=s.sink, keep=s.keep_first)
         if (tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and self.lanes == s.value_dim
-                and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS and s.keep_first == 0):
+                and self.lanes in ops.TCGEN05_ATTENTION_HEAD_DIMS):
             # bf16 prompts with heads of 64 or 128 lanes: scores and outputs in tensor memory (tcgen05)
             ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids, n_seqs=ctx.n_seqs,
                                   max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads, d=self.lanes, page_size=PAGE_SIZE,
                                   scale=s.scale, window=s.window or 0, ring_pages=view.kv_group.ring_pages,
-                                  softcap=s.softcap or 0.0, sink=s.sink)
+                                  softcap=s.softcap or 0.0, sink=s.sink, keep=s.keep_first)
             return o
         if tensor_cores and ctx.max_q_len > 1:
             # other bf16 prompts and portions: the mma.sync form

@@ -313,6 +313,9 @@ def _attention_with_kept_keys(kind, q, keys, values, scale, window, keep, past, 
     elif kind == "tensor":
         ops.attention_capped(*args, n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d, dv=dv, page_size=64, ring_pages=code,
                              window=window, scale=scale, keep=keep)
+    elif kind == "tensor memory":
+        ops.attention_tcgen05(*args, n_seqs=1, max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64, ring_pages=code,
+                              window=window, scale=scale, keep=keep)
     else:
         ops.attention_capped_decode(*args, n_seqs=1, nq=nq, nkv=nkv, d=d, dv=dv, page_size=64, ring_pages=code, window=window,
                                     scale=scale, splits=splits, partial=partial, keep=keep)
@@ -326,17 +329,17 @@ KEPT_CASES = [  # window, keep, total length, tokens of the step, ring pages, pi
 
 
 @pytest.mark.parametrize("kind,dtype", [("cores", torch.float32), ("cores", torch.bfloat16), ("tensor", torch.bfloat16),
-                                        ("decode", torch.bfloat16)])
+                                        ("decode", torch.bfloat16), ("tensor memory", torch.bfloat16)])
 @pytest.mark.parametrize("window,keep,L,T,ring,pinned,splits", KEPT_CASES)
 def test_attention_that_keeps_the_first_positions(kind, dtype, window, keep, L, T, ring, pinned, splits):
     """Against the plain masked softmax, on pages laid out as the cache lays them out (positions that left the ring are
     overwritten).  One query head asks sharply for the oldest key of its window, one for the key just outside it, one
     for the last kept position and one for the first position that is not kept: a key dropped or kept by mistake moves
     the output by the size of a value."""
-    if kind == "decode" and T != 1 or kind == "tensor" and splits > 1:
-        pytest.skip("the single-token form takes one token; the form for prompts does not cut the keys")
+    if kind == "decode" and T != 1 or kind in ("tensor", "tensor memory") and splits > 1:
+        pytest.skip("the single-token form takes one token; the forms for prompts do not cut the keys")
     gen = torch.Generator().manual_seed(window * 1000 + keep + L)
-    nq, nkv, d, dv = 4, 2, 32, 16
+    nq, nkv, d, dv = (4, 2, 64, 64) if kind == "tensor memory" else (4, 2, 32, 16)
     keys = torch.randn(L, nkv, d, generator=gen)
     keys = keys / keys.norm(dim=-1, keepdim=True)
     values = torch.randn(L, nkv, dv, generator=gen)
