@@ -11,7 +11,7 @@
 //  scan        per sequence and head h (group g = h / (heads / G)), over the sequence's tokens in order:
 //                dt = softplus(dt_raw + dt_bias[h]);  S <- exp(-exp(A_log[h]) dt) S + dt B_g x_h^T;  y = S^T C_g + D[h] x_h
 //              with S [N, P] fp32 per (sequence, head), kept in the cache between steps.  A block owns 32 columns of S;
-//              a column lives in the registers of 8 lanes, the read-out is a sum over those lanes; 16 tokens of B, C, x
+//              a column lives in the registers of 8 or 16 lanes, the read-out is a sum over those lanes; 16 tokens of B, C, x
 //              and the decays are staged in shared memory at a time, the next 16 by asynchronous copies meanwhile.
 //  gate_norm   v = y * silu(z); v is RMS-normed in `norm_groups` equal parts of a token's row (each part by its own
 //              root mean square, eps inside the root), times a weight per lane, rounded once to T.
@@ -23,7 +23,6 @@
 #define SSD_MAX_TAPS 16
 #define SSD_TCH 16          // tokens staged at a time
 #define SSD_COLS 32         // most columns of S per block (a kernel form takes 32 or 8)
-#define SSD_LANES 8         // lanes that share a column
 
 struct SsdArgs {
   const void* proj;       // [n_tokens, ld] in T
@@ -102,28 +101,29 @@ __device__ __forceinline__ void ssd_cp16(float* dst, const float* src) {
 __device__ __forceinline__ void ssd_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void ssd_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// NPT: rows of S per lane (N <= 8 NPT).  VEC (N a multiple of 4, 16-byte aligned rows of xbc): a lane owns rows
-// 4 (ns + 8 j) .. + 3 of its column and reads B and C four at a time; else rows ns + 8 k, one at a time.
+// LANES: lanes that share a column of S (8 or 16); NPT: rows of S per lane (N <= LANES NPT).  VEC (N a multiple of 4,
+// 16-byte aligned rows of xbc): a lane owns rows 4 (ns + LANES j) .. + 3 of its column and reads B and C four at a time;
+// else rows ns + LANES k, one at a time.
 // Two staging buffers: while the block works through one chunk of SSD_TCH tokens, the asynchronous copies of the next
 // chunk's B, C and x (and the loads of its step sizes) are in flight; one barrier per chunk.
 // COLS: columns of S per block (COLS * 8 threads): fewer columns make more blocks, which is what a step of one long
 // sequence needs, since each warp's time is the chain of its tokens.
-template <typename T, int NPT, bool VEC, int COLS>
-__global__ void __launch_bounds__(COLS * SSD_LANES)
+template <typename T, int NPT, bool VEC, int COLS, int LANES>
+__global__ void __launch_bounds__(COLS * LANES)
 ssd_scan_kernel(SsdArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float ssd_smem[];
   const int N = a.N, P = a.P, inner = a.heads * P, C = inner + 2 * a.G * N;
   const int stage = SSD_TCH * (2 * N + COLS) + 2 * SSD_TCH;      // floats of one buffer
-  const int tid = threadIdx.x, ns = tid % SSD_LANES, pc = tid / SSD_LANES;
+  const int tid = threadIdx.x, ns = tid % LANES, pc = tid / LANES;
   const int h = blockIdx.y, seq = blockIdx.z, g = h / (a.heads / a.G);
   const int p0 = blockIdx.x * COLS, p = p0 + pc;
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
   if (q_len <= 0) return;
   const int slot = a.slots[seq];
   float* S = a.state + ((size_t)slot * a.heads + h) * N * P;
-  auto row_of = [&](int k) { return VEC ? 4 * (ns + SSD_LANES * (k >> 2)) + (k & 3) : ns + SSD_LANES * k; };
+  auto row_of = [&](int k) { return VEC ? 4 * (ns + LANES * (k >> 2)) + (k & 3) : ns + LANES * k; };
   float s[NPT];
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
@@ -139,20 +139,16 @@ ssd_scan_kernel(SsdArgs a) {
     float* buf = ssd_smem + (size_t)(c & 1) * stage;
     const int base = c * SSD_TCH, nt = min(SSD_TCH, q_len - base);
     const float* rows = a.xbc + (size_t)(q_begin + base) * C;
-    if (VEC) {
-      const int n4 = N / 4;
-      for (int i = tid; i < nt * n4; i += blockDim.x) {
-        const int tt = i / n4, j = (i % n4) * 4;
-        const float* src = rows + (size_t)tt * C + inner + (size_t)g * N + j;
-        ssd_cp16(buf + tt * N + j, src);
-        ssd_cp16(buf + SSD_TCH * N + tt * N + j, src + (size_t)a.G * N);
-      }
-    } else {
-      for (int i = tid; i < nt * N; i += blockDim.x) {
-        const int tt = i / N, n = i % N;
-        const float* src = rows + (size_t)tt * C + inner + (size_t)g * N + n;
-        ssd_cp4(buf + tt * N + n, src);
-        ssd_cp4(buf + SSD_TCH * N + tt * N + n, src + (size_t)a.G * N);
+    // a warp copies a token's B and C rows, token after token (no division in the loop)
+    const int warp = tid >> 5, lane = tid & 31, n_warps = (COLS * LANES) >> 5;
+    for (int tt = warp; tt < nt; tt += n_warps) {
+      const float* src = rows + (size_t)tt * C + inner + (size_t)g * N;
+      float* dB = buf + tt * N;
+      float* dC = buf + SSD_TCH * N + tt * N;
+      if (VEC) {
+        for (int j = 4 * lane; j < N; j += 128) { ssd_cp16(dB + j, src + j); ssd_cp16(dC + j, src + (size_t)a.G * N + j); }
+      } else {
+        for (int n = lane; n < N; n += 32) { ssd_cp4(dB + n, src + n); ssd_cp4(dC + n, src + (size_t)a.G * N + n); }
       }
     }
     float* sX = buf + 2 * SSD_TCH * N;
@@ -200,7 +196,7 @@ ssd_scan_kernel(SsdArgs a) {
       if (VEC) {
 #pragma unroll
         for (int j = 0; j < NPT / 4; ++j) {
-          const int n = 4 * (ns + SSD_LANES * j);
+          const int n = 4 * (ns + LANES * j);
           if (FULL || n < N) {
             const float4 b = *(const float4*)(B + n), cv = *(const float4*)(Cc + n);
             s[4 * j] = fmaf(da, s[4 * j], dx * b.x);         acc[0] = fmaf(s[4 * j], cv.x, acc[0]);
@@ -212,7 +208,7 @@ ssd_scan_kernel(SsdArgs a) {
       } else {
 #pragma unroll
         for (int k = 0; k < NPT; ++k) {
-          const int n = ns + SSD_LANES * k;
+          const int n = ns + LANES * k;
           if (FULL || n < N) {
             s[k] = fmaf(da, s[k], dx * B[n]);
             acc[k & 3] = fmaf(s[k], Cc[n], acc[k & 3]);
@@ -220,14 +216,53 @@ ssd_scan_kernel(SsdArgs a) {
         }
       }
       float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       if (ns == 0 && p < P) a.y[(size_t)(q_begin + base + tt) * inner + (size_t)h * P + p] = fmaf(dskip, x, sum);
     };
-    if (N == SSD_LANES * NPT) {
-#pragma unroll 2
-      for (int tt = 0; tt < nt; ++tt) token(tt, std::true_type{});
+    // four tokens at a time: the state goes through them in order, their four read-outs are summed over the column's
+    // lanes side by side, so that the shuffles' latency is paid once per four tokens (full states, VEC form)
+    auto tokens4 = [&](int t0) {
+      float x[4], dx[4], da[4], acc[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        x[u] = sX[(t0 + u) * COLS + pc];
+        dx[u] = sDt[t0 + u] * x[u];
+        da[u] = sDa[t0 + u];
+        acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < NPT / 4; ++j) {
+        const int n = 4 * (ns + LANES * j);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float4 b = *(const float4*)(sB + (t0 + u) * N + n), cv = *(const float4*)(sC + (t0 + u) * N + n);
+          s[4 * j] = fmaf(da[u], s[4 * j], dx[u] * b.x);         acc[u][0] = fmaf(s[4 * j], cv.x, acc[u][0]);
+          s[4 * j + 1] = fmaf(da[u], s[4 * j + 1], dx[u] * b.y); acc[u][1] = fmaf(s[4 * j + 1], cv.y, acc[u][1]);
+          s[4 * j + 2] = fmaf(da[u], s[4 * j + 2], dx[u] * b.z); acc[u][2] = fmaf(s[4 * j + 2], cv.z, acc[u][2]);
+          s[4 * j + 3] = fmaf(da[u], s[4 * j + 3], dx[u] * b.w); acc[u][3] = fmaf(s[4 * j + 3], cv.w, acc[u][3]);
+        }
+      }
+      float sum[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sum[u] = (acc[u][0] + acc[u][1]) + (acc[u][2] + acc[u][3]);
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], o);
+      }
+      if (ns == 0 && p < P) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          a.y[(size_t)(q_begin + base + t0 + u) * inner + (size_t)h * P + p] = fmaf(dskip, x[u], sum[u]);
+      }
+    };
+    if (N == LANES * NPT) {
+      int tt = 0;
+      if (VEC) {
+        for (; tt + 4 <= nt; tt += 4) tokens4(tt);
+      }
+      for (; tt < nt; ++tt) token(tt, std::true_type{});
     } else {
       for (int tt = 0; tt < nt; ++tt) token(tt, std::false_type{});
     }
@@ -271,7 +306,10 @@ static int ssd_launch(const SsdArgs& a, cudaStream_t stream) {
   odi_rc = launch_pdl((ssd_conv_kernel<T>), dim3(a.n_tokens, (C + 255) / 256), dim3(256), 0, stream, a);
   if (odi_rc == 0 && a.taps > 1)
     odi_rc = launch_pdl((ssd_conv_state_kernel<T>), dim3(a.n_seqs, (C + 255) / 256), dim3(256), 0, stream, a);
-  // 32 columns a block when that already gives two blocks per multiprocessor, else 8
+  // Two forms: 32 columns a block when that already gives two blocks per multiprocessor (many sequences); else 8
+  // columns, four times the blocks, since a warp's time is the chain of its sequence's tokens and a step of one long
+  // sequence has nothing else to run beside it.  (Measured at 32 heads of 64 columns, 128 rows, 2,048 tokens: 32
+  // columns 1,080 us, 8 columns 545 us, 8 columns over 16 lanes each 640 us.)
   const bool narrow = (long)((a.P + 31) / 32) * a.heads * a.n_seqs < 2 * 148;
   const int cols = narrow ? 8 : SSD_COLS;
   const dim3 grid((a.P + cols - 1) / cols, a.heads, a.n_seqs);
@@ -279,15 +317,15 @@ static int ssd_launch(const SsdArgs& a, cudaStream_t stream) {
   const int C_all = a.heads * a.P + 2 * a.G * a.N;
   const bool vec = a.N % 4 == 0 && C_all % 4 == 0 && (a.heads * a.P) % 4 == 0 && ((uintptr_t)a.xbc & 15) == 0;
   if (odi_rc == 0) {
-#define ODI_SCAN_FORM(NPT, VEC, COLS) \
+#define ODI_SCAN_FORM(NPT, VEC, COLS, LANES) \
     do { if (smem > 48 * 1024) { \
-           const cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, VEC, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+           const cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, NPT, VEC, COLS, LANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
            if (e != cudaSuccess) return (int)e; } \
-         odi_rc = launch_pdl((ssd_scan_kernel<T, NPT, VEC, COLS>), grid, dim3(COLS * SSD_LANES), smem, stream, a); } while (0)
-#define ODI_SCAN(NPT) \
-    do { if (vec) { if (narrow) ODI_SCAN_FORM(NPT, true, 8); else ODI_SCAN_FORM(NPT, true, 32); } \
-         else { if (narrow) ODI_SCAN_FORM(NPT, false, 8); else ODI_SCAN_FORM(NPT, false, 32); } } while (0)
-    if (a.N <= 32) ODI_SCAN(4); else if (a.N <= 64) ODI_SCAN(8); else if (a.N <= 128) ODI_SCAN(16); else ODI_SCAN(32);
+         odi_rc = launch_pdl((ssd_scan_kernel<T, NPT, VEC, COLS, LANES>), grid, dim3(COLS * LANES), smem, stream, a); } while (0)
+#define ODI_SCAN(NPT_WIDE, NPT_NARROW) \
+    do { if (vec) { if (narrow) ODI_SCAN_FORM(NPT_NARROW, true, 8, 8); else ODI_SCAN_FORM(NPT_WIDE, true, 32, 8); } \
+         else { if (narrow) ODI_SCAN_FORM(NPT_NARROW, false, 8, 8); else ODI_SCAN_FORM(NPT_WIDE, false, 32, 8); } } while (0)
+    if (a.N <= 32) ODI_SCAN(4, 4); else if (a.N <= 64) ODI_SCAN(8, 8); else if (a.N <= 128) ODI_SCAN(16, 16); else ODI_SCAN(32, 32);
 #undef ODI_SCAN
 #undef ODI_SCAN_FORM
   }
