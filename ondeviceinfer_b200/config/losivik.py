@@ -16,8 +16,8 @@
   experts of ``expert.ff`` lanes with the squared ReLU, ``router.top`` chosen by the largest sigmoid scores, which
   multiply the experts' inputs; ``shared.ff``: one more expert that every token takes.
 
-Every layer is x <- x + ls1 * mixer(norm1(x)) + ls2 * ff(norm2(x)) with norms whose weights are stored around zero,
-followed by a per-layer input looked up by token id (``side.*``).  The embedding is scaled and gets sinusoidal
+Every layer is x <- x + ls1 * mixer(norm1(x)) + ls2 * ff(norm2(x)) with RMS norms that multiply by one plus their
+stored weight, followed by a per-layer input looked up by token id (``side.*``).  The embedding is scaled and gets sinusoidal
 positions; the head is the embedding table.  A key that is absent switches its mechanism off.
 Tensor names: ``embed``, ``side.embed``, ``l<i>.norm1|norm2|ls1|ls2``, ``l<i>.mix.*``, ``l<i>.mlp.*``,
 ``l<i>.side.gate|proj|norm``, ``final.norm``.

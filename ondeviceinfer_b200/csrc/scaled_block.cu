@@ -101,13 +101,44 @@ scaled_add2_kernel(float* __restrict__ x, const float* __restrict__ a, const flo
   if (copy != nullptr) copy[i] = from_f<T>(v);
 }
 
+// Four lanes a thread (H a multiple of 4, aligned tensors): the same arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scaled_add2_vec_kernel(float4* __restrict__ x, const float4* __restrict__ a, const float4* __restrict__ s1, const float4* __restrict__ b,
+                       const float4* __restrict__ s2, T* __restrict__ copy, long n4, int H4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const int lane = (int)(i % H4);
+  float4 v = x[i];
+  const float4 av = a[i], sv = s1[lane];
+  v.x = fmaf(av.x, sv.x, v.x); v.y = fmaf(av.y, sv.y, v.y); v.z = fmaf(av.z, sv.z, v.z); v.w = fmaf(av.w, sv.w, v.w);
+  if (b != nullptr) {
+    const float4 bv = b[i], tv = s2[lane];
+    v.x = fmaf(bv.x, tv.x, v.x); v.y = fmaf(bv.y, tv.y, v.y); v.z = fmaf(bv.z, tv.z, v.z); v.w = fmaf(bv.w, tv.w, v.w);
+  }
+  x[i] = v;
+  if (copy != nullptr) {
+    T* c = copy + i * 4;
+    c[0] = from_f<T>(v.x); c[1] = from_f<T>(v.y); c[2] = from_f<T>(v.z); c[3] = from_f<T>(v.w);
+  }
+}
+
 extern "C" int odi_scaled_add2(float* x, const float* a, const float* s1, const float* b, const float* s2, void* copy, long rows,
                                int H, int dtype, cudaStream_t stream) {
   const long n = rows * H;
   if (n <= 0) return 0;
+  if (b != nullptr && s2 == nullptr) return ODI_ERR_ARGUMENT;
+  if (H % 4 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)s1 | (uintptr_t)b | (uintptr_t)s2 | (uintptr_t)copy) & 15) == 0) {
+    const long n4 = n / 4, vblocks = (n4 + 255) / 256;
+    if (vblocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
+    if (dtype == 0) odi_rc = launch_pdl((scaled_add2_vec_kernel<float>), dim3((unsigned)vblocks), dim3(256), 0, stream, (float4*)x, (const float4*)a, (const float4*)s1, (const float4*)b, (const float4*)s2, (float*)copy, n4, H / 4);
+    else odi_rc = launch_pdl((scaled_add2_vec_kernel<bf16>), dim3((unsigned)vblocks), dim3(256), 0, stream, (float4*)x, (const float4*)a, (const float4*)s1, (const float4*)b, (const float4*)s2, (bf16*)copy, n4, H / 4);
+    return launch_status();
+  }
   const long blocks = (n + 255) / 256;
   if (blocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
-  if (b != nullptr && s2 == nullptr) return ODI_ERR_ARGUMENT;
   if (dtype == 0) odi_rc = launch_pdl((scaled_add2_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, stream, x, a, s1, b, s2, (float*)copy, n, H);
   else odi_rc = launch_pdl((scaled_add2_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, stream, x, a, s1, b, s2, (bf16*)copy, n, H);
   return launch_status();
@@ -121,8 +152,24 @@ weighted_sum_kernel(float* __restrict__ out, const float* __restrict__ a, const 
   if (i < n) out[i] = fmaf(cb, b[i], ca * a[i]);
 }
 
+__global__ void __launch_bounds__(256)
+weighted_sum_vec_kernel(float4* __restrict__ out, const float4* __restrict__ a, const float4* __restrict__ b, long n4, float ca, float cb) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 av = a[i], bv = b[i];
+  out[i] = make_float4(fmaf(cb, bv.x, ca * av.x), fmaf(cb, bv.y, ca * av.y), fmaf(cb, bv.z, ca * av.z), fmaf(cb, bv.w, ca * av.w));
+}
+
 extern "C" int odi_weighted_sum(float* out, const float* a, const float* b, long n, float ca, float cb, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (n % 4 == 0 && (((uintptr_t)out | (uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+    const long vblocks = (n / 4 + 255) / 256;
+    if (vblocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
+    odi_rc = launch_pdl(weighted_sum_vec_kernel, dim3((unsigned)vblocks), dim3(256), 0, stream, (float4*)out, (const float4*)a, (const float4*)b, n / 4, ca, cb);
+    return launch_status();
+  }
   const long blocks = (n + 255) / 256;
   if (blocks > 2147483647L) return ODI_ERR_UNSUPPORTED;
   odi_rc = launch_pdl(weighted_sum_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, out, a, b, n, ca, cb);

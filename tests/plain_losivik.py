@@ -33,7 +33,7 @@ def rms_divide(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def norm_around_zero(x, w, eps):
+def norm_one_plus(x, w, eps):
     return rms_divide(x, eps) * (1.0 + w)
 
 
@@ -177,7 +177,7 @@ def forward(cfg, weights, tokens, keep_layers=False):
     streams = []
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
-        h = norm_around_zero(x, w[p + "norm1"], eps)
+        h = norm_one_plus(x, w[p + "norm1"], eps)
         if layer["type"] == "latent_attention":
             mixed = latent_attention(w, p + "mix.", m, h, eps)
         else:
@@ -186,14 +186,14 @@ def forward(cfg, weights, tokens, keep_layers=False):
         update = mixed * w[p + "ls1"]
         f = layer.get("mlp")
         if f is not None:
-            h = norm_around_zero(x, w[p + "norm2"], eps)
+            h = norm_one_plus(x, w[p + "norm2"], eps)
             fed = dense_feed_forward(w, p + "mlp.", f, h) if f["kind"] == "dense" else routed_feed_forward(w, p + "mlp.", f, h)
             update = update + fed * w[p + "ls2"]
         x = x + update
         if cfg.get("token_side"):
             x = x + token_side_input(w, cfg, i, x, tokens)
         streams.append(x.clone())
-    logits = norm_around_zero(x, w["final.norm"], eps) @ w["embed"].T
+    logits = norm_one_plus(x, w["final.norm"], eps) @ w["embed"].T
     return (logits, torch.stack(streams)) if keep_layers else logits
 
 

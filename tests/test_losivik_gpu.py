@@ -112,8 +112,8 @@ def test_two_norms_in_one_pass_and_the_scaled_add(dtype, rows, width):
     w1, w2 = torch.randn(width, generator=gen) * 0.2, torch.randn(width, generator=gen) * 0.2
     o1, o2 = torch.empty(rows, width, dtype=dtype, device="cuda"), torch.empty(rows, width, dtype=dtype, device="cuda")
     ops.dual_norm(x.cuda(), (1 + w1).cuda(), (1 + w2).cuda(), 1e-5, o1, o2)
-    torch.testing.assert_close(o1.cpu().double(), plain.norm_around_zero(x.double(), w1.double(), 1e-5), **tol(dtype))
-    torch.testing.assert_close(o2.cpu().double(), plain.norm_around_zero(x.double(), w2.double(), 1e-5), **tol(dtype))
+    torch.testing.assert_close(o1.cpu().double(), plain.norm_one_plus(x.double(), w1.double(), 1e-5), **tol(dtype))
+    torch.testing.assert_close(o2.cpu().double(), plain.norm_one_plus(x.double(), w2.double(), 1e-5), **tol(dtype))
     a, b = torch.randn(rows, width, generator=gen), torch.randn(rows, width, generator=gen)
     for second in (True, False):
         stream, copy_ = x.clone().cuda(), torch.empty(rows, width, dtype=dtype, device="cuda")
