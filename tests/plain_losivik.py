@@ -253,6 +253,16 @@ TINY_C = _config(120, 64, [
     {"type": "latent_attention", "mixer": _latent(4, 16, 16, 16, 0.25, 65), "mlp": _moe(4, 2, 32, 16)},
     {"type": "parallel", "mixer": _pair(2, 1, 32, 16, 0.18, 129, 1, 2, 32, 8, 1, 2, 1), "mlp": _dense(32, 3.0)},
 ])
+# sizes in the middle: heads of 96 and 80 lanes, latent rows of 160, which take other kernel forms than the small ones
+TINY_D = _config(200, 160, [
+    {"type": "latent_attention", "mixer": _latent(5, 96, 80, 160, 0.1, 100), "mlp": _moe(4, 2, 64, 32)},
+    {"type": "parallel", "mixer": _pair(6, 3, 96, 80, 0.1, 90, 10, 5, 24, 80, 5, 2, 1), "mlp": _dense(200, 1.0)},
+], scale=0.8, side=24)
+# heads of 128 lanes on both sides: the kernels that keep scores in tensor memory, with kept first positions
+TINY_E = _config(150, 128, [
+    {"type": "parallel", "mixer": _pair(4, 2, 128, 128, 0.09, 70, 3, 4, 32, 64, 2, 4, 2), "mlp": _dense(96, 1.5)},
+    {"type": "latent_attention", "mixer": _latent(2, 128, 128, 64, 0.09, 100), "mlp": _moe(3, 2, 48)},
+], scale=1.2, side=16)
 # sharpened softmaxes: a layer of each attention kind with windows of hundreds of positions
 SHARP = _config(90, 64, [
     {"type": "parallel", "mixer": _pair(4, 2, 16, 16, 0.25, 200, 40, 2, 16, 8, 1, 2, 1), "mlp": None},

@@ -14,7 +14,7 @@ from ondeviceinfer_b200.config.specs import (CappedAttentionSpec, ClampedGatedML
 from ondeviceinfer_b200.engine.model import DecoderModel
 from ondeviceinfer_b200.registry import config_from_dict
 
-CONFIGS = {"A": plain.TINY_A, "B": plain.TINY_B, "C": plain.TINY_C, "sharp": plain.SHARP}
+CONFIGS = {"A": plain.TINY_A, "B": plain.TINY_B, "C": plain.TINY_C, "D": plain.TINY_D, "E": plain.TINY_E, "sharp": plain.SHARP}
 
 
 @pytest.mark.parametrize("case", sorted(CONFIGS))

@@ -25,7 +25,8 @@ from ondeviceinfer_b200.kernels import ops
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = {"A": (plain.TINY_A, 51), "B": (plain.TINY_B, 52), "C": (plain.TINY_C, 53), "sharp": (plain.SHARP, 54)}
+CONFIGS = {"A": (plain.TINY_A, 51), "B": (plain.TINY_B, 52), "C": (plain.TINY_C, 53), "sharp": (plain.SHARP, 54),
+           "D": (plain.TINY_D, 55), "E": (plain.TINY_E, 56)}
 SHARPEN = {"sharp": 3.0}
 _MODELS, _PLAIN = {}, {}
 
@@ -374,7 +375,7 @@ def test_attention_that_keeps_the_first_positions(kind, dtype, window, keep, L, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_whole_prompts_and_their_first_tokens(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -420,7 +421,7 @@ def test_residual_stream_after_every_layer(case, dtype, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_prompt_then_single_tokens_over_page_and_window_borders(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -438,7 +439,7 @@ def test_prompt_then_single_tokens_over_page_and_window_borders(case, dtype, tmp
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_portions_of_several_sizes_down_to_two_tokens(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
@@ -454,7 +455,7 @@ def test_portions_of_several_sizes_down_to_two_tokens(case, dtype, tmp_path_fact
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_on_slots_and_pages_used_again(case, dtype, tmp_path_factory):
     model = engine(case, dtype, tmp_path_factory)
     cfg = CONFIGS[case][0]
